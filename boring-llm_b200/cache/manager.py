@@ -19,10 +19,15 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple, Union
 @dataclass(frozen=True)
 class PagedKVSpec:
     """What a mixer that caches keys and values needs: `window` 0 keeps every key, n > 0 only the
-    last n positions (the query's own included)."""
+    last n positions (the query's own included). `v_head_dim` 0: values have the keys' head size."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim if self.v_head_dim > 0 else self.head_dim
 
 
 @dataclass(frozen=True)

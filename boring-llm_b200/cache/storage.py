@@ -2,7 +2,9 @@
 
 For every paged group one tensor `[layers in group, 2 (keys, values), pages + 1, kv heads, page size,
 head size]`: the rows of one (page, kv head) lie together, so a kernel reads a page of one head as
-one contiguous tile. For every state group one tensor `[layers in group, request slots, *shape]`.
+one contiguous tile. A group whose values have another head size than its keys has two tensors instead
+(`[layers in group, pages + 1, kv heads, page size, head size]` each); `keys()` / `values()` give a layer's
+pages either way. For every state group one tensor `[layers in group, request slots, *shape]`.
 Keys are stored after rotation, values as projected (src/model.br:1814-1820).
 """
 from __future__ import annotations
@@ -25,11 +27,20 @@ class CacheStorage:
         # size (captured CUDA graphs) write there, where no request ever reads.
         self.trash_page = manager.num_pages
         self.trash_slot = manager.max_requests
-        self.kv: List[torch.Tensor] = []
+        self.kv: List[torch.Tensor] = []           # joint tensors (groups with two tensors have None here)
+        self.k_pages: List[torch.Tensor] = []      # per group [layers, pages + 1, kv heads, page size, head size]
+        self.v_pages: List[torch.Tensor] = []
         for g in manager.paged_groups:
-            self.kv.append(torch.zeros(
-                (len(g.cache_layers), 2, manager.num_pages + 1, g.spec.n_kv_heads, manager.page_size,
-                 g.spec.head_dim), dtype=kv_dtype, device=self.device))
+            lead = (manager.num_pages + 1, g.spec.n_kv_heads, manager.page_size)
+            if g.spec.value_dim == g.spec.head_dim:
+                kv = torch.zeros((len(g.cache_layers), 2) + lead + (g.spec.head_dim,), dtype=kv_dtype, device=self.device)
+                self.kv.append(kv)
+                self.k_pages.append(kv[:, 0])
+                self.v_pages.append(kv[:, 1])
+            else:
+                self.kv.append(None)
+                self.k_pages.append(torch.zeros((len(g.cache_layers),) + lead + (g.spec.head_dim,), dtype=kv_dtype, device=self.device))
+                self.v_pages.append(torch.zeros((len(g.cache_layers),) + lead + (g.spec.value_dim,), dtype=kv_dtype, device=self.device))
         self.state: List[torch.Tensor] = []
         for sg in manager.state_groups:
             self.state.append(torch.zeros(
@@ -43,14 +54,16 @@ class CacheStorage:
         otherwise left as they are, because nothing may read a request's cache past its length; with poison a
         kernel that does read there, even with weight zero, turns its output into NaN. Returns the pages filled."""
         n = 0
-        for g, kv in zip(self.manager.paged_groups, self.kv):
+        for gi, g in enumerate(self.manager.paged_groups):
             if g.pool.freed_log is None:
                 g.pool.freed_log = []
                 pages = [p for p in range(g.pool.num_pages) if g.pool.owner_of(p) is None] + [self.trash_page]
             else:
                 pages, g.pool.freed_log = [p for p in set(g.pool.freed_log) if g.pool.owner_of(p) is None], []
-            if pages and kv.dtype.is_floating_point:
-                kv[:, :, torch.tensor(pages, dtype=torch.long, device=self.device)] = float("nan")
+            if pages and self.kv_dtype.is_floating_point:
+                idx = torch.tensor(pages, dtype=torch.long, device=self.device)
+                self.k_pages[gi][:, idx] = float("nan")
+                self.v_pages[gi][:, idx] = float("nan")
                 n += len(pages)
         return n
 
@@ -61,12 +74,12 @@ class CacheStorage:
     def keys(self, cache_layer: int) -> torch.Tensor:
         kind, gi, li = self.manager.layer_location[cache_layer]
         assert kind == "paged"
-        return self.kv[gi][li, 0]
+        return self.k_pages[gi][li]
 
     def values(self, cache_layer: int) -> torch.Tensor:
         kind, gi, li = self.manager.layer_location[cache_layer]
         assert kind == "paged"
-        return self.kv[gi][li, 1]
+        return self.v_pages[gi][li]
 
     def layer_state(self, cache_layer: int) -> torch.Tensor:
         """`[request slots, *shape]` of one cache layer with fixed-size state."""
@@ -75,4 +88,4 @@ class CacheStorage:
         return self.state[gi][li]
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.kv + self.state)
+        return sum(t.numel() * t.element_size() for t in self.k_pages + self.v_pages + self.state)

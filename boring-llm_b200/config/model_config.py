@@ -201,11 +201,13 @@ class Qwen2Config:
 
 
 def architecture_name(d: dict) -> str:
-    """The name the registry dispatches on: `architectures[0]`, else `model_type`
-    (role of `general.architecture`, src/model.br:381)."""
+    """The name the registry dispatches on: `architectures[0]`, else `architecture` (a plain string), else
+    `model_type` (role of `general.architecture`, src/model.br:381)."""
     archs = d.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
+    if isinstance(d.get("architecture"), str):
+        return d["architecture"]
     mt = d.get("model_type")
     if isinstance(mt, str):
         return mt

@@ -181,6 +181,71 @@ int bl_gemm_tc_splitk(const void* x, const void* w, const void* bias, int bias_d
                       int M, int N, int K, int epilogue, void* stream);
 int bl_gemm_tc_splitk_status(int* status);
 
+// The plain product with rows of x that are `ldx` values apart (a column range of a wider matrix as the input).
+int bl_gemm_plain_ld(const void* x, int x_dtype, int ldx, const void* w, int w_dtype, const void* bias, int bias_dtype,
+                     void* out, int out_dtype, int M, int N, int K, int epilogue, void* stream);
+
+// bl_attention_plain with options: values of head size dv (keys and queries: dh); sinks[H] (null: none): exp(sinks[h])
+// joins head h's softmax denominator once, unscaled, without a value; gate (null: none): head h of token t is
+// multiplied by sigmoid(gate[t * ld_gate + h]). out: [T, H * dv].
+int bl_attention_plain_ext(const void* q, const void* k_cache, const void* v_cache, int dtype,
+                           const int* tok_req, const int* cu_q, const int* ctx_len, const int* block_table,
+                           int max_pages, void* out, int T, int H, int KV, int dh, int dv, int page_size, int window,
+                           float scale, const void* sinks, int sink_dtype, const float* gate, int ld_gate, void* stream);
+
+// y[r, :] = (x[src, :] - mean) / sqrt(var + eps) * w + b (b may be null), src = row_idx ? row_idx[r] : r; var is the
+// mean of the squared deviations; statistics in 32-bit.
+int bl_layernorm(const float* x, const int* row_idx, const void* w, int w_dtype, const void* b, int b_dtype,
+                 void* y, int y_dtype, int rows, int d, float eps, void* stream);
+// x[r, :] += layer norm(sub[r, :] * sigmoid(gate[r * ld_gate + :])) * w + b: a gate on a sublayer's result, the norm
+// behind the sublayer and the residual sum. gate and b may be null.
+int bl_gated_norm_residual(float* x, const float* sub, const float* gate, int ld_gate, const void* w, int w_dtype,
+                           const void* b, int b_dtype, int rows, int d, float eps, void* stream);
+// out[e] = sum_{j < n} coeffs[j] * streams[j * stride + e], e < count.
+int bl_depth_mix(const float* streams, long long stride, const void* coeffs, int c_dtype, int n, float* out,
+                 long long count, void* stream);
+// y[e] = act(x[e]) (y may be x).
+#define BL_ACT_SILU 0
+#define BL_ACT_GELU_ERF 1
+#define BL_ACT_GELU_TANH 2
+int bl_activation(const void* x, int x_dtype, void* y, int y_dtype, long long count, int act, void* stream);
+
+// Rows proj[T, ld] hold a token's joined projections: q in columns 0 .. H * dk, k from off_k (KV * dk), v from off_v
+// (KV * dv). RMS norm of the whole q row and of the whole k row (weights q_norm_w [H * dk], k_norm_w [KV * dk]; null:
+// no norm), rotation of the first 2 * rot_half dimensions of every head by angle float(position) * inv_freq[j], q to
+// q_out [T, H * dk], k and v into the pages of the token's request (null caches: not written).
+int bl_qk_norm_rope_write(const float* proj, int ld, int off_k, int off_v, const void* q_norm_w, int qw_dtype,
+                          const void* k_norm_w, int kw_dtype, float eps, const int* positions, const int* tok_req,
+                          const int* block_table, int max_pages, const float* inv_freq, int rot_half, int pair_layout,
+                          void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int KV, int dk, int dv,
+                          int page_size, void* stream);
+
+// Linear recurrences over a matrix state per head kept in state slots (recurrent.cu). Request r owns tokens
+// cu_q[r] .. cu_q[r + 1] - 1 and the slot slots[r]; its state S [H, dk, dv] starts at state + slots[r] * slot_stride.
+// q, k: [T, G * dk] (query/key head of head h: h / (H / G)), v: [T, H * dv], z: [T, H * dk] (the decay's
+// pre-activation: a = exp(-coef[h] * softplus(z_sign * z))), beta: [T, H] logits (delta rule only), each with its own
+// row stride; out: [T, H * dv] 32-bit.
+#define BL_RULE_GLA 0      // S <- diag(a) S + k v^T; o = S^T (q * q_scale)
+#define BL_RULE_DELTA 1    // S <- diag(a) S; u = sigmoid(beta) (v - S^T k); S <- S + k u^T; o = S^T (q * q_scale)
+int bl_recurrent_scan(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                      const float* z, int ldz, const float* beta, int ldb, const float* coef, float z_sign,
+                      float q_scale, float* state, long long slot_stride, const int* slots, const int* cu_q, int R,
+                      float* out, int H, int G, int dk, int dv, void* stream);
+// y[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[:] * gate(g[t * ld_gate + h * dv + :]) (gate null: none).
+#define BL_GATE_SIGMOID 0
+#define BL_GATE_SILU 1
+int bl_head_norm_gate(const float* o, const void* w, int w_dtype, const float* gate, int ld_gate, int gate_kind,
+                      void* y, int y_dtype, int T, int H, int dv, float eps, void* stream);
+// y[t, ch] = silu(sum_i taps[ch, i] * x[t - (n_taps - 1) + i, ch]) over a request's tokens, the inputs before the
+// step's first token taken from the slot's tail [n_taps - 1, C] (oldest first); then heads 0 .. unit_heads - 1 of dk
+// columns become unit vectors (x / sqrt(sum x^2 + unit_eps)), the first scaled_heads of them times q_scale.
+int bl_conv_silu_unit(const float* x, int ld, const float* taps, int n_taps, const float* tail, long long slot_stride,
+                      const int* slots, const int* tok_req, const int* cu_q, float* y, int T, int C, int unit_heads,
+                      int scaled_heads, int dk, float q_scale, float unit_eps, void* stream);
+// The tail of every request with tokens becomes its last n_taps - 1 inputs (after bl_conv_silu_unit has read it).
+int bl_conv_tail_update(const float* x, int ld, int n_taps, float* tail, long long slot_stride, const int* slots,
+                        const int* cu_q, int R, int C, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -5,6 +5,9 @@
 // (src/math.br:327-328); online form as FlashAttnKernel (src/math_gpu.br:3224-3287).
 // A (token, head) is computed the same way whatever else is in the batch: its chunks of 32 keys start
 // at its first visible key. This is the 32-bit path's attention and the twin of the fast kernels.
+// Options (bl_attention_plain_ext): values of another head size than the keys; a sink per head, a learned score that
+// joins the softmax's denominator once, unscaled, without a value; a gate per (token, head) whose sigmoid multiplies
+// the head's output.
 #include "common.cuh"
 #include "api.h"
 
@@ -18,8 +21,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_plain_kernel(const TT* __restrict__ q, const TT* __restrict__ kc, const TT* __restrict__ vc,
                        const int* __restrict__ tok_req, const int* __restrict__ cu_q,
                        const int* __restrict__ ctx_len, const int* __restrict__ block_table, int max_pages,
-                       TT* __restrict__ out, int T, int H, int KV, int dh, int page_size, int window,
-                       float scale) {
+                       TT* __restrict__ out, int T, int H, int KV, int dh, int dv, int page_size, int window,
+                       float scale, const void* __restrict__ sinks, int sink_dtype, const float* gate, int ld_gate) {
     __shared__ float qs[WARPS][MAX_DH];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * WARPS + warp;
@@ -34,8 +37,8 @@ attention_plain_kernel(const TT* __restrict__ q, const TT* __restrict__ kc, cons
     for (int d = lane; d < dh; d += 32) qs[warp][d] = bl_load(qrow + d);
     __syncwarp();
     const int* bt = block_table + (size_t)r * max_pages;
-    const size_t head_off = (size_t)kvh * page_size * dh;
-    const size_t page_stride = (size_t)KV * page_size * dh;
+    const size_t head_off = (size_t)kvh * page_size * dh, v_head_off = (size_t)kvh * page_size * dv;
+    const size_t page_stride = (size_t)KV * page_size * dh, v_page_stride = (size_t)KV * page_size * dv;
     float m = -INFINITY, l = 0.f;
     float acc[MAX_DH / 32];
 #pragma unroll
@@ -62,21 +65,30 @@ attention_plain_kernel(const TT* __restrict__ q, const TT* __restrict__ kc, cons
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int key = base + jj;
             const int page = bt[key / page_size];
-            const TT* vrow = vc + (size_t)page * page_stride + head_off + (size_t)(key % page_size) * dh;
+            const TT* vrow = vc + (size_t)page * v_page_stride + v_head_off + (size_t)(key % page_size) * dv;
 #pragma unroll
             for (int i = 0; i < MAX_DH / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < dh) acc[i] = fmaf(pj, bl_load(vrow + d), acc[i]);
+                if (d < dv) acc[i] = fmaf(pj, bl_load(vrow + d), acc[i]);
             }
         }
         m = m_new;
     }
-    TT* orow = out + ((size_t)t * H + h) * dh;
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    if (sinks) {                                       // one more term of the denominator, after the last key
+        const float sk = bl_load_any(sinks, sink_dtype, h);
+        const float m_new = fmaxf(m, sk);
+        const float alpha = expf(m - m_new);
+        l = l * alpha + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < MAX_DH / 32; ++i) acc[i] *= alpha;
+    }
+    TT* orow = out + ((size_t)t * H + h) * dv;
+    float inv = l > 0.f ? 1.0f / l : 0.f;
+    if (gate) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * ld_gate + h]));
 #pragma unroll
     for (int i = 0; i < MAX_DH / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < dh) bl_store(orow + d, acc[i] * inv);
+        if (d < dv) bl_store(orow + d, acc[i] * inv);
     }
 }
 
@@ -86,7 +98,18 @@ extern "C" int bl_attention_plain(const void* q, const void* k_cache, const void
                                   const int* tok_req, const int* cu_q, const int* ctx_len,
                                   const int* block_table, int max_pages, void* out, int T, int H, int KV,
                                   int dh, int page_size, int window, float scale, void* stream) {
+    return bl_attention_plain_ext(q, k_cache, v_cache, dtype, tok_req, cu_q, ctx_len, block_table, max_pages, out, T, H, KV,
+                                  dh, dh, page_size, window, scale, nullptr, 0, nullptr, 0, stream);
+}
+
+extern "C" int bl_attention_plain_ext(const void* q, const void* k_cache, const void* v_cache, int dtype,
+                                      const int* tok_req, const int* cu_q, const int* ctx_len,
+                                      const int* block_table, int max_pages, void* out, int T, int H, int KV,
+                                      int dh, int dv, int page_size, int window, float scale, const void* sinks,
+                                      int sink_dtype, const float* gate, int ld_gate, void* stream) {
     if (T <= 0) return 0;
+    if (dv <= 0 || dv > MAX_DH) BL_FAIL("bl_attention_plain: value head size %d is outside 1..%d", dv, MAX_DH);
+    if (gate && ld_gate < H) BL_FAIL("bl_attention_plain: gate rows of %d hold fewer than %d heads", ld_gate, H);
     if (H <= 0 || KV <= 0 || H % KV != 0) BL_FAIL("bl_attention_plain: %d heads cannot share %d key/value heads", H, KV);
     if (dh <= 0 || dh > MAX_DH) BL_FAIL("bl_attention_plain: head size %d is outside 1..%d", dh, MAX_DH);
     if (page_size <= 0 || max_pages <= 0 || window < 0) BL_FAIL("bl_attention_plain: bad page size, table width or window");
@@ -94,12 +117,12 @@ extern "C" int bl_attention_plain(const void* q, const void* k_cache, const void
     const int blocks = (T * H + WARPS - 1) / WARPS;
     if (dtype == BL_F32)
         attention_plain_kernel<float><<<blocks, WARPS * 32, 0, s>>>((const float*)q, (const float*)k_cache,
-            (const float*)v_cache, tok_req, cu_q, ctx_len, block_table, max_pages, (float*)out, T, H, KV, dh,
-            page_size, window, scale);
+            (const float*)v_cache, tok_req, cu_q, ctx_len, block_table, max_pages, (float*)out, T, H, KV, dh, dv,
+            page_size, window, scale, sinks, sink_dtype, gate, ld_gate);
     else if (dtype == BL_BF16)
         attention_plain_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, s>>>((const __nv_bfloat16*)q,
             (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, tok_req, cu_q, ctx_len, block_table,
-            max_pages, (__nv_bfloat16*)out, T, H, KV, dh, page_size, window, scale);
+            max_pages, (__nv_bfloat16*)out, T, H, KV, dh, dv, page_size, window, scale, sinks, sink_dtype, gate, ld_gate);
     else
         BL_FAIL("bl_attention_plain: unknown dtype %d", dtype);
     BL_CHECK_LAUNCH("bl_attention_plain");

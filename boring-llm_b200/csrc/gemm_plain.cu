@@ -14,7 +14,7 @@ constexpr int TM = 64, TN = 64, TK = 16;
 template <typename TX, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void* __restrict__ bias,
-                  int bias_dtype, TO* __restrict__ out, int M, int N, int K) {
+                  int bias_dtype, TO* __restrict__ out, int M, int N, int K, int ldx) {
     __shared__ float xs[TK][TM + 1];
     __shared__ float ws[TK][TN + 1];
     __shared__ float us[EPI == BL_EPI_SWIGLU ? TK : 1][TN + 1];
@@ -26,7 +26,7 @@ gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void
         for (int i = threadIdx.x; i < TM * TK; i += 256) {
             const int r = i / TK, c = i % TK;
             const int m = m0 + r, k = k0 + c;
-            xs[c][r] = (m < M && k < K) ? bl_load(x + (size_t)m * K + k) : 0.f;
+            xs[c][r] = (m < M && k < K) ? bl_load(x + (size_t)m * ldx + k) : 0.f;
         }
         for (int i = threadIdx.x; i < TN * TK; i += 256) {
             const int r = i / TK, c = i % TK;
@@ -77,10 +77,10 @@ gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void
 
 template <typename TX, typename TW, typename TO>
 int launch_epi(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
-               int M, int N, int K, int epi, cudaStream_t s) {
+               int M, int N, int K, int ldx, int epi, cudaStream_t s) {
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
 #define BL_GO(E) gemm_plain_kernel<TX, TW, TO, E><<<grid, 256, 0, s>>>( \
-        (const TX*)x, (const TW*)w, bias, bias_dtype, (TO*)out, M, N, K)
+        (const TX*)x, (const TW*)w, bias, bias_dtype, (TO*)out, M, N, K, ldx)
     switch (epi) {
         case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
         case BL_EPI_BIAS: BL_GO(BL_EPI_BIAS); break;
@@ -95,11 +95,11 @@ int launch_epi(const void* x, const void* w, const void* bias, int bias_dtype, v
 
 template <typename TX, typename TW>
 int launch_out(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
-               int M, int N, int K, int epi, cudaStream_t s) {
-    if (out_dtype == BL_F32) return launch_epi<TX, TW, float>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
+               int M, int N, int K, int ldx, int epi, cudaStream_t s) {
+    if (out_dtype == BL_F32) return launch_epi<TX, TW, float>(x, w, bias, bias_dtype, out, M, N, K, ldx, epi, s);
     if (out_dtype == BL_BF16) {
         if (epi == BL_EPI_RESIDUAL) BL_FAIL("bl_gemm_plain: the residual stream is 32-bit; output dtype must be float32");
-        return launch_epi<TX, TW, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
+        return launch_epi<TX, TW, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, ldx, epi, s);
     }
     BL_FAIL("bl_gemm_plain: unknown output dtype %d", out_dtype);
 }
@@ -109,17 +109,24 @@ int launch_out(const void* x, const void* w, const void* bias, int bias_dtype, v
 extern "C" int bl_gemm_plain(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias,
                              int bias_dtype, void* out, int out_dtype, int M, int N, int K, int epilogue,
                              void* stream) {
+    return bl_gemm_plain_ld(x, x_dtype, K, w, w_dtype, bias, bias_dtype, out, out_dtype, M, N, K, epilogue, stream);
+}
+
+extern "C" int bl_gemm_plain_ld(const void* x, int x_dtype, int ldx, const void* w, int w_dtype, const void* bias,
+                                int bias_dtype, void* out, int out_dtype, int M, int N, int K, int epilogue,
+                                void* stream) {
     if (M <= 0) return 0;
+    if (ldx < K) BL_FAIL("bl_gemm_plain: rows of x are %d apart but hold %d values", ldx, K);
     if (N <= 0 || K <= 0) BL_FAIL("bl_gemm_plain: bad sizes N=%d K=%d", N, K);
     if (epilogue == BL_EPI_BIAS && bias == nullptr) BL_FAIL("bl_gemm_plain: bias epilogue without a bias");
     if (epilogue == BL_EPI_BIAS && bias_dtype != BL_F32 && bias_dtype != BL_BF16)
         BL_FAIL("bl_gemm_plain: unknown bias dtype %d", bias_dtype);
     cudaStream_t s = (cudaStream_t)stream;
     if (x_dtype == BL_F32 && w_dtype == BL_F32)
-        return launch_out<float, float>(x, w, bias, bias_dtype, out, out_dtype, M, N, K, epilogue, s);
+        return launch_out<float, float>(x, w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, epilogue, s);
     if (x_dtype == BL_BF16 && w_dtype == BL_BF16)
-        return launch_out<__nv_bfloat16, __nv_bfloat16>(x, w, bias, bias_dtype, out, out_dtype, M, N, K, epilogue, s);
+        return launch_out<__nv_bfloat16, __nv_bfloat16>(x, w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, epilogue, s);
     if (x_dtype == BL_F32 && w_dtype == BL_BF16)
-        return launch_out<float, __nv_bfloat16>(x, w, bias, bias_dtype, out, out_dtype, M, N, K, epilogue, s);
+        return launch_out<float, __nv_bfloat16>(x, w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, epilogue, s);
     BL_FAIL("bl_gemm_plain: unsupported input dtypes x=%d w=%d", x_dtype, w_dtype);
 }

@@ -1,0 +1,272 @@
+// Linear recurrences with a matrix state per head, S [key channels, value channels], carried per request in a state
+// slot, for prompts' portions and single decoded tokens alike (a request's tokens are cu_q[r] .. cu_q[r + 1] - 1 of
+// the batch; a request without tokens is left alone). Two rules share one kernel:
+//   gated linear attention   S <- diag(a) S + k v^T;                                   o = S^T q
+//   gated delta rule         S <- diag(a) S;  u = beta (v - S^T k);  S <- S + k u^T;   o = S^T q
+// with a decay per key channel a = exp(-coef[head] * softplus(sign * z)) from the decay's pre-activation z (sign -1,
+// coef 1 / tau gives sigmoid(z)^(1 / tau)). State, decays, gates and all sums are 32-bit. The columns of S are
+// independent of one another, so a block owns a few columns of one (request, head) and walks the request's tokens in
+// order; a column's rows are spread over KS lanes of a warp that add up with a fixed butterfly. What a token's result is
+// does not depend on the batch or on how the tokens were cut into steps.
+// Also here: the short causal convolution + SiLU + unit norm in front of the delta rule, the hand-over of the
+// convolution's last inputs to the state slot, and the per-head RMS norm with an output gate behind both rules.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int RKMAX = 16;          // rows of a column that one lane holds
+constexpr int MAX_TAPS = 16;
+constexpr int SCAN_SMEM_BYTES = 40 * 1024;
+
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+template <bool DELTA>
+__global__ void __launch_bounds__(WARPS * 32)
+recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z, int ldz,
+                      const float* beta, int ldb, const float* __restrict__ coef, float z_sign, float q_scale,
+                      float* state, size_t slot_stride, const int* __restrict__ slots, const int* __restrict__ cu_q,
+                      float* out, int H, int G, int dk, int dv, int KS, int chunk) {
+    extern __shared__ float sm[];
+    const int r = blockIdx.z, h = blockIdx.y;
+    const int t0 = cu_q[r], n = cu_q[r + 1] - t0;
+    if (n <= 0) return;
+    const int gh = h / (H / G);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int CW = 32 / KS, cols_blk = WARPS * CW;
+    const int s = lane / CW, cc = lane % CW;
+    const int c = (blockIdx.x * WARPS + warp) * CW + cc;
+    const bool col_ok = c < dv;
+    float* sq = sm;                          // [chunk, dk] q * q_scale
+    float* sk = sq + (size_t)chunk * dk;     // [chunk, dk]
+    float* sd = sk + (size_t)chunk * dk;     // [chunk, dk] decay
+    float* sv = sd + (size_t)chunk * dk;     // [chunk, cols_blk]
+    float* sb = sv + (size_t)chunk * cols_blk;   // [chunk] beta
+    float* S = state + (size_t)slots[r] * slot_stride + (size_t)h * dk * dv;
+    float st[RKMAX];
+#pragma unroll
+    for (int i = 0; i < RKMAX; ++i) {
+        const int row = i * KS + s;
+        st[i] = (row < dk && col_ok) ? S[(size_t)row * dv + c] : 0.f;
+    }
+    const float cf = coef[h];
+    for (int base = 0; base < n; base += chunk) {
+        const int m = min(chunk, n - base);
+        for (int idx = threadIdx.x; idx < m * dk; idx += WARPS * 32) {
+            const int tt = idx / dk, d = idx % dk;
+            const size_t tok = (size_t)(t0 + base + tt);
+            sq[idx] = q[tok * ldq + gh * dk + d] * q_scale;
+            sk[idx] = k[tok * ldk + gh * dk + d];
+            sd[idx] = expf(-cf * softplusf_(z_sign * z[tok * ldz + h * dk + d]));
+        }
+        for (int idx = threadIdx.x; idx < m * cols_blk; idx += WARPS * 32) {
+            const int tt = idx / cols_blk, j = idx % cols_blk;
+            const int col = blockIdx.x * cols_blk + j;
+            sv[idx] = col < dv ? v[(size_t)(t0 + base + tt) * ldv + h * dv + col] : 0.f;
+        }
+        if (DELTA)
+            for (int tt = threadIdx.x; tt < m; tt += WARPS * 32) sb[tt] = sigmoidf_(beta[(size_t)(t0 + base + tt) * ldb + h]);
+        __syncthreads();
+        for (int tt = 0; tt < m; ++tt) {
+            const float* pq = sq + (size_t)tt * dk;
+            const float* pk = sk + (size_t)tt * dk;
+            const float* pd = sd + (size_t)tt * dk;
+            const float vv = sv[tt * cols_blk + warp * CW + cc];
+            float o;
+            if (!DELTA) {
+                o = 0.f;
+#pragma unroll
+                for (int i = 0; i < RKMAX; ++i) {
+                    const int row = i * KS + s;
+                    if (row < dk) {
+                        st[i] = fmaf(pd[row], st[i], pk[row] * vv);
+                        o = fmaf(st[i], pq[row], o);
+                    }
+                }
+                for (int x = 16; x >= CW; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+            } else {
+                float sk_ = 0.f, sq_ = 0.f, kq = 0.f;
+#pragma unroll
+                for (int i = 0; i < RKMAX; ++i) {
+                    const int row = i * KS + s;
+                    if (row < dk) {
+                        st[i] *= pd[row];
+                        sk_ = fmaf(st[i], pk[row], sk_);
+                        sq_ = fmaf(st[i], pq[row], sq_);
+                        kq = fmaf(pk[row], pq[row], kq);
+                    }
+                }
+                for (int x = 16; x >= CW; x >>= 1) {
+                    sk_ += __shfl_xor_sync(0xffffffffu, sk_, x);
+                    sq_ += __shfl_xor_sync(0xffffffffu, sq_, x);
+                    kq += __shfl_xor_sync(0xffffffffu, kq, x);
+                }
+                const float u = sb[tt] * (vv - sk_);
+#pragma unroll
+                for (int i = 0; i < RKMAX; ++i) {
+                    const int row = i * KS + s;
+                    if (row < dk) st[i] = fmaf(pk[row], u, st[i]);
+                }
+                o = fmaf(kq, u, sq_);                  // S^T q after the write: (a S)^T q + (k . q) u
+            }
+            if (s == 0 && col_ok) out[(size_t)(t0 + base + tt) * H * dv + h * dv + c] = o;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < RKMAX; ++i) {
+        const int row = i * KS + s;
+        if (row < dk && col_ok) S[(size_t)row * dv + c] = st[i];
+    }
+}
+
+// y[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[:] * gate(g[t, h, :]); one warp per (token, head).
+template <typename TY>
+__global__ void __launch_bounds__(WARPS * 32)
+head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, const float* gate, int ld_gate, int gate_kind,
+                      TY* __restrict__ y, int items, int H, int dv, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int t = item / H, h = item % H;
+    const float* src = o + (size_t)item * dv;
+    float ss = 0.f;
+    for (int i = lane; i < dv; i += 32) ss += src[i] * src[i];
+    const float inv = 1.0f / sqrtf(bl_warp_sum(ss) / (float)dv + eps);
+    const float* g = gate ? gate + (size_t)t * ld_gate + h * dv : nullptr;
+    for (int i = lane; i < dv; i += 32) {
+        float val = src[i] * inv * bl_load_any(w, w_dtype, i);
+        if (g) val *= gate_kind == BL_GATE_SILU ? bl_silu(g[i]) : sigmoidf_(g[i]);
+        bl_store(y + (size_t)item * dv + i, val);
+    }
+}
+
+// One block per token: y[t, ch] = silu(sum_i taps[ch, i] * x[t - (n_taps - 1) + i, ch]), the inputs before the step's
+// first token of the request coming from the slot's tail (its last n_taps - 1 inputs, oldest first; zeros at the
+// start of a sequence). Then the first `unit_heads` heads of `dk` columns are made unit vectors, x / sqrt(sum x^2 +
+// unit_eps), the first `scaled_heads` of them also times q_scale.
+__global__ void __launch_bounds__(WARPS * 32)
+conv_silu_unit_kernel(const float* x, int ld, const float* __restrict__ taps, int n_taps, const float* tail, size_t slot_stride,
+                      const int* __restrict__ slots, const int* __restrict__ tok_req, const int* __restrict__ cu_q, float* y,
+                      int C, int unit_heads, int scaled_heads, int dk, float q_scale, float unit_eps) {
+    const int t = blockIdx.x;
+    const int r = tok_req[t];
+    const int j = t - cu_q[r];
+    const float* tl = tail + (size_t)slots[r] * slot_stride;
+    for (int ch = threadIdx.x; ch < C; ch += WARPS * 32) {
+        float acc = 0.f;
+        for (int i = 0; i < n_taps; ++i) {
+            const int off = j - (n_taps - 1) + i;
+            const float xv = off >= 0 ? x[(size_t)(t - j + off) * ld + ch] : tl[(size_t)(n_taps - 1 + off) * C + ch];
+            acc = fmaf(taps[(size_t)ch * n_taps + i], xv, acc);
+        }
+        y[(size_t)t * C + ch] = bl_silu(acc);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    for (int hh = threadIdx.x >> 5; hh < unit_heads; hh += WARPS) {
+        float* p = y + (size_t)t * C + (size_t)hh * dk;
+        float ss = 0.f;
+        for (int d = lane; d < dk; d += 32) ss += p[d] * p[d];
+        const float inv = (hh < scaled_heads ? q_scale : 1.f) / sqrtf(bl_warp_sum(ss) + unit_eps);
+        for (int d = lane; d < dk; d += 32) p[d] *= inv;
+    }
+}
+
+// After the step's convolutions have read the tail: the last n_taps - 1 inputs of each request with tokens.
+__global__ void conv_tail_update_kernel(const float* x, int ld, int n_taps, float* tail, size_t slot_stride,
+                                        const int* __restrict__ slots, const int* __restrict__ cu_q, int C) {
+    const int r = blockIdx.y;
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t0 = cu_q[r], n = cu_q[r + 1] - t0;
+    if (n <= 0 || ch >= C) return;
+    float* tl = tail + (size_t)slots[r] * slot_stride;
+    float keep[MAX_TAPS];
+#pragma unroll
+    for (int i = 0; i < MAX_TAPS; ++i) {
+        if (i < n_taps - 1) {
+            const int off = n - (n_taps - 1) + i;
+            keep[i] = off >= 0 ? x[(size_t)(t0 + off) * ld + ch] : tl[(size_t)(n_taps - 1 + off) * C + ch];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_TAPS; ++i)
+        if (i < n_taps - 1) tl[(size_t)i * C + ch] = keep[i];
+}
+
+}  // namespace
+
+extern "C" int bl_recurrent_scan(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                                 const float* z, int ldz, const float* beta, int ldb, const float* coef, float z_sign,
+                                 float q_scale, float* state, long long slot_stride, const int* slots, const int* cu_q, int R,
+                                 float* out, int H, int G, int dk, int dv, void* stream) {
+    if (R <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G != 0 || dk <= 0 || dv <= 0) BL_FAIL("bl_recurrent_scan: bad sizes H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
+    if (dk > RKMAX * 32) BL_FAIL("bl_recurrent_scan: %d key channels, at most %d", dk, RKMAX * 32);
+    if (R > 65535 || H > 65535) BL_FAIL("bl_recurrent_scan: %d requests or %d heads are too many for one launch", R, H);
+    if (rule == BL_RULE_DELTA && beta == nullptr) BL_FAIL("bl_recurrent_scan: the delta rule needs beta");
+    int KS = 1;
+    while ((dk + KS - 1) / KS > RKMAX) KS *= 2;
+    const int CW = 32 / KS, cols_blk = WARPS * CW;
+    const size_t per_token = (size_t)(3 * dk + cols_blk + 1) * sizeof(float);
+    int chunk = (int)(SCAN_SMEM_BYTES / per_token);
+    chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
+    const size_t smem = per_token * chunk;
+    if (smem > 48 * 1024) BL_FAIL("bl_recurrent_scan: %d key channels need %zu bytes of shared memory a token", dk, per_token);
+    dim3 grid((dv + cols_blk - 1) / cols_blk, H, R);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (rule == BL_RULE_GLA)
+        recurrent_scan_kernel<false><<<grid, WARPS * 32, smem, s>>>(q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, coef, z_sign, q_scale,
+            state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk);
+    else if (rule == BL_RULE_DELTA)
+        recurrent_scan_kernel<true><<<grid, WARPS * 32, smem, s>>>(q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, coef, z_sign, q_scale,
+            state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk);
+    else
+        BL_FAIL("bl_recurrent_scan: unknown rule %d", rule);
+    BL_CHECK_LAUNCH("bl_recurrent_scan");
+    return 0;
+}
+
+extern "C" int bl_head_norm_gate(const float* o, const void* w, int w_dtype, const float* gate, int ld_gate, int gate_kind,
+                                 void* y, int y_dtype, int T, int H, int dv, float eps, void* stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || dv <= 0 || (gate && ld_gate < H * dv)) BL_FAIL("bl_head_norm_gate: bad sizes H=%d dv=%d gate stride %d", H, dv, ld_gate);
+    if (gate && gate_kind != BL_GATE_SIGMOID && gate_kind != BL_GATE_SILU) BL_FAIL("bl_head_norm_gate: unknown gate %d", gate_kind);
+    const int items = T * H, blocks = (items + WARPS - 1) / WARPS;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (y_dtype == BL_F32)
+        head_norm_gate_kernel<float><<<blocks, WARPS * 32, 0, s>>>(o, w, w_dtype, gate, ld_gate, gate_kind, (float*)y, items, H, dv, eps);
+    else if (y_dtype == BL_BF16)
+        head_norm_gate_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, s>>>(o, w, w_dtype, gate, ld_gate, gate_kind,
+                                                                            (__nv_bfloat16*)y, items, H, dv, eps);
+    else
+        BL_FAIL("bl_head_norm_gate: unknown output dtype %d", y_dtype);
+    BL_CHECK_LAUNCH("bl_head_norm_gate");
+    return 0;
+}
+
+extern "C" int bl_conv_silu_unit(const float* x, int ld, const float* taps, int n_taps, const float* tail, long long slot_stride,
+                                 const int* slots, const int* tok_req, const int* cu_q, float* y, int T, int C, int unit_heads,
+                                 int scaled_heads, int dk, float q_scale, float unit_eps, void* stream) {
+    if (T <= 0) return 0;
+    if (n_taps < 1 || n_taps > MAX_TAPS) BL_FAIL("bl_conv_silu_unit: %d taps, 1..%d are built", n_taps, MAX_TAPS);
+    if (C <= 0 || ld < C || unit_heads * dk > C || scaled_heads > unit_heads)
+        BL_FAIL("bl_conv_silu_unit: bad sizes C=%d ld=%d heads=%d of %d", C, ld, unit_heads, dk);
+    conv_silu_unit_kernel<<<T, WARPS * 32, 0, (cudaStream_t)stream>>>(x, ld, taps, n_taps, tail, (size_t)slot_stride, slots, tok_req,
+                                                                      cu_q, y, C, unit_heads, scaled_heads, dk, q_scale, unit_eps);
+    BL_CHECK_LAUNCH("bl_conv_silu_unit");
+    return 0;
+}
+
+extern "C" int bl_conv_tail_update(const float* x, int ld, int n_taps, float* tail, long long slot_stride, const int* slots,
+                                   const int* cu_q, int R, int C, void* stream) {
+    if (R <= 0 || n_taps <= 1) return 0;
+    if (n_taps > MAX_TAPS) BL_FAIL("bl_conv_tail_update: %d taps, 1..%d are built", n_taps, MAX_TAPS);
+    if (R > 65535) BL_FAIL("bl_conv_tail_update: %d requests are too many for one launch", R);
+    dim3 grid((C + 127) / 128, R);
+    conv_tail_update_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, ld, n_taps, tail, (size_t)slot_stride, slots, cu_q, C);
+    BL_CHECK_LAUNCH("bl_conv_tail_update");
+    return 0;
+}

@@ -154,14 +154,17 @@ def add_row_vector(x: torch.Tensor, v: torch.Tensor) -> None:
 
 def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
                epilogue: int = EPI_NONE) -> None:
-    """out = epilogue(x @ w.T) on CUDA cores with 32-bit accumulation."""
+    """out = epilogue(x @ w.T) on CUDA cores with 32-bit accumulation. x may be a range of columns of a wider
+    row-major matrix (its rows `x.stride(0)` values apart)."""
     M, K = x.shape
     N = out.shape[1]
     rows_w = 2 * N if epilogue == EPI_SWIGLU else N
-    _need(x, "x"); _need(w, "w", None, (rows_w, K)); _need(out, "out", None, (M, N))
+    if not x.is_cuda or x.stride(1) != 1 or x.stride(0) < K:
+        raise KernelError("x: must be a CUDA matrix whose rows are contiguous")
+    _need(w, "w", None, (rows_w, K)); _need(out, "out", None, (M, N))
     if bias is not None:
         _need(bias, "bias", None, (N,))
-    _call(_lib().bl_gemm_plain, _p(x), _dt(x), _p(w), _dt(w), _p(bias), _dt(bias) if bias is not None else 0,
+    _call(_lib().bl_gemm_plain_ld, _p(x), _dt(x), x.stride(0), _p(w), _dt(w), _p(bias), _dt(bias) if bias is not None else 0,
           _p(out), _dt(out), M, N, K, epilogue, _stream())
 
 
@@ -235,16 +238,29 @@ def qkv_rope_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
 
 def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_req: torch.Tensor,
                     cu_q: torch.Tensor, ctx_len: torch.Tensor, block_table: torch.Tensor,
-                    out: torch.Tensor, H: int, window: int, scale: float) -> None:
-    """Paged causal grouped-query attention, one warp per (token, head)."""
+                    out: torch.Tensor, H: int, window: int, scale: float, sinks: Optional[torch.Tensor] = None,
+                    gate: Optional[torch.Tensor] = None) -> None:
+    """Paged causal grouped-query attention, one warp per (token, head). The values' head size may differ from the
+    keys' (v_cache `[pages, kv heads, page, dv]`, out `[T, H * dv]`). `sinks` [H]: exp(sinks[h]) joins head h's softmax
+    denominator (once, unscaled, no value). `gate` (32-bit, [T, >= H], rows contiguous, possibly a column range of a
+    wider matrix): head h of token t is multiplied by sigmoid(gate[t, h])."""
     T = q.shape[0]
-    _, KV, page_size, dh = k_cache.shape
-    _need(q, "q", k_cache.dtype, (T, H * dh)); _need(k_cache, "k_cache"); _need(v_cache, "v_cache", k_cache.dtype, k_cache.shape)
+    n_pages, KV, page_size, dh = k_cache.shape
+    dv = v_cache.shape[3]
+    _need(q, "q", k_cache.dtype, (T, H * dh)); _need(k_cache, "k_cache")
+    _need(v_cache, "v_cache", k_cache.dtype, (n_pages, KV, page_size, dv))
     _need(tok_req, "tok_req", torch.int32, (T,)); _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32)
-    _need(block_table, "block_table", torch.int32); _need(out, "out", q.dtype, (T, H * dh))
-    _call(_lib().bl_attention_plain, _p(q), _p(k_cache), _p(v_cache), _dt(q), _p(tok_req), _p(cu_q),
-          _p(ctx_len), _p(block_table), block_table.shape[1], _p(out), T, H, KV, dh, page_size, window,
-          ctypes.c_float(scale), _stream())
+    _need(block_table, "block_table", torch.int32); _need(out, "out", q.dtype, (T, H * dv))
+    if sinks is not None:
+        _need(sinks, "sinks", None, (H,))
+    ld_gate = 0
+    if gate is not None:
+        if not gate.is_cuda or gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < H:
+            raise KernelError("gate: must be 32-bit CUDA rows [T, >= H] with contiguous rows")
+        ld_gate = gate.stride(0)
+    _call(_lib().bl_attention_plain_ext, _p(q), _p(k_cache), _p(v_cache), _dt(q), _p(tok_req), _p(cu_q),
+          _p(ctx_len), _p(block_table), block_table.shape[1], _p(out), T, H, KV, dh, dv, page_size, window,
+          ctypes.c_float(scale), _p(sinks), _dt(sinks) if sinks is not None else 0, _p(gate), ld_gate, _stream())
 
 
 def argmax(logits: torch.Tensor, out_ids: torch.Tensor) -> None:
@@ -735,3 +751,160 @@ def norm_qkv_rope(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w_qkv: torc
           _dt(bias) if bias is not None else 0, _p(positions), _p(tok_req), _p(block_table), block_table.shape[1],
           _p(inv_freq), ctypes.c_float(mscale), _p(q_out), _p(k_cache), _p(v_cache), M, K, H, KV, dh, page_size,
           pair_layout, _stream())
+
+
+# ---- norms with bias, gated residuals, the average over the layers' streams ----------------------------------------
+ACT_SILU, ACT_GELU_ERF, ACT_GELU_TANH = 0, 1, 2
+GATE_SIGMOID, GATE_SILU = 0, 1
+RULE_GLA, RULE_DELTA = 0, 1
+
+
+def _rows32(t: torch.Tensor, name: str, rows: int, min_cols: int) -> int:
+    """Checks 32-bit CUDA rows that may be a column range of a wider matrix; returns their row stride."""
+    if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1 or t.shape[0] != rows or t.shape[1] < min_cols:
+        raise KernelError(f"{name}: must be 32-bit CUDA rows [{rows}, >= {min_cols}] with contiguous rows, got {tuple(t.shape)} {t.dtype}")
+    return t.stride(0)
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out: torch.Tensor,
+              row_idx: Optional[torch.Tensor] = None) -> None:
+    """out[r] = (x[src] - mean) / sqrt(var + eps) * weight + bias, src = row_idx[r] if given else r; 32-bit statistics."""
+    d = x.shape[1]
+    rows = out.shape[0]
+    _need(x, "x", torch.float32); _need(weight, "weight", None, (d,)); _need(out, "out", None, (rows, d))
+    if bias is not None:
+        _need(bias, "bias", None, (d,))
+    if row_idx is not None:
+        _need(row_idx, "row_idx", torch.int32, (rows,))
+    elif x.shape[0] != rows:
+        raise KernelError("layernorm: x and out differ in rows")
+    _call(_lib().bl_layernorm, _p(x), _p(row_idx), _p(weight), _dt(weight), _p(bias), _dt(bias) if bias is not None else 0,
+          _p(out), _dt(out), rows, d, ctypes.c_float(eps), _stream())
+
+
+def gated_norm_residual(x: torch.Tensor, sub: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor,
+                        bias: Optional[torch.Tensor], eps: float) -> None:
+    """x += layer norm(sub * sigmoid(gate)) * weight + bias, row by row, in 32-bit (gate None: no gate)."""
+    rows, d = x.shape
+    _need(x, "x", torch.float32); _need(sub, "sub", torch.float32, (rows, d)); _need(weight, "weight", None, (d,))
+    if bias is not None:
+        _need(bias, "bias", None, (d,))
+    ld = _rows32(gate, "gate", rows, d) if gate is not None else 0
+    _call(_lib().bl_gated_norm_residual, _p(x), _p(sub), _p(gate), ld, _p(weight), _dt(weight), _p(bias),
+          _dt(bias) if bias is not None else 0, rows, d, ctypes.c_float(eps), _stream())
+
+
+def depth_mix(streams: torch.Tensor, coeffs: torch.Tensor, n: int, out: torch.Tensor) -> None:
+    """out = sum_{j < n} coeffs[j] * streams[j]; streams [>= n, T, d] 32-bit, out [T, d] (it may be a later stream)."""
+    _need(streams, "streams", torch.float32); _need(out, "out", torch.float32, tuple(streams.shape[1:]))
+    _need(coeffs, "coeffs")
+    if not (0 < n <= streams.shape[0] and coeffs.numel() >= n):
+        raise KernelError(f"depth_mix: {n} streams asked of {streams.shape[0]} with {coeffs.numel()} coefficients")
+    _call(_lib().bl_depth_mix, _p(streams), ctypes.c_longlong(streams.stride(0)), _p(coeffs), _dt(coeffs), n, _p(out),
+          ctypes.c_longlong(out.numel()), _stream())
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, act: int) -> None:
+    """out = silu, the exact (erf) gelu or the tanh gelu of every element of x, evaluated in 32-bit (out may be x)."""
+    _need(x, "x"); _need(out, "out", None, tuple(x.shape))
+    _call(_lib().bl_activation, _p(x), _dt(x), _p(out), _dt(out), ctypes.c_longlong(x.numel()), act, _stream())
+
+
+def qk_norm_rope_write(proj: torch.Tensor, off_k: int, off_v: int, q_norm_w: Optional[torch.Tensor],
+                       k_norm_w: Optional[torch.Tensor], eps: float, positions: torch.Tensor, tok_req: torch.Tensor,
+                       block_table: torch.Tensor, inv_freq: torch.Tensor, rot_half: int, pair_layout: int, q_out: torch.Tensor,
+                       k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], H: int, KV: int, dk: int, dv: int) -> None:
+    """From a token's joined projections (32-bit rows: q first, k from column off_k, v from off_v): RMS norm over the
+    whole q row and the whole k row (weights None: no norm), rotation, q out, k and v into the request's pages."""
+    T = proj.shape[0]
+    ld = _rows32(proj, "proj", T, off_v + KV * dv)
+    _need(positions, "positions", torch.int32, (T,)); _need(tok_req, "tok_req", torch.int32, (T,))
+    _need(block_table, "block_table", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
+    if inv_freq.numel() < rot_half:
+        raise KernelError("inv_freq: fewer entries than rotated pairs")
+    _need(q_out, "q_out", None, (T, H * dk))
+    if q_norm_w is not None:
+        _need(q_norm_w, "q_norm_w", None, (H * dk,))
+    if k_norm_w is not None:
+        _need(k_norm_w, "k_norm_w", None, (KV * dk,))
+    page_size = 1
+    if k_cache is not None:
+        _need(k_cache, "k_cache", q_out.dtype); _need(v_cache, "v_cache", q_out.dtype)
+        if tuple(k_cache.shape[1:]) != (KV, k_cache.shape[2], dk) or tuple(v_cache.shape) != (k_cache.shape[0], KV, k_cache.shape[2], dv):
+            raise KernelError(f"caches {tuple(k_cache.shape)} / {tuple(v_cache.shape)} do not hold {KV} heads of {dk} / {dv}")
+        page_size = k_cache.shape[2]
+    _call(_lib().bl_qk_norm_rope_write, _p(proj), ld, off_k, off_v, _p(q_norm_w), _dt(q_norm_w) if q_norm_w is not None else 0,
+          _p(k_norm_w), _dt(k_norm_w) if k_norm_w is not None else 0, ctypes.c_float(eps), _p(positions), _p(tok_req),
+          _p(block_table), block_table.shape[1], _p(inv_freq), rot_half, pair_layout, _p(q_out), _p(k_cache), _p(v_cache),
+          _dt(q_out), T, H, KV, dk, dv, page_size, _stream())
+
+
+def recurrent_scan(rule: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, beta: Optional[torch.Tensor],
+                   coef: torch.Tensor, z_sign: float, q_scale: float, state: torch.Tensor, slots: torch.Tensor,
+                   cu_q: torch.Tensor, out: torch.Tensor, H: int, G: int, dk: int, dv: int) -> None:
+    """A linear recurrence over a matrix state per head and request (`RULE_GLA`, `RULE_DELTA`; see `bl_recurrent_scan`).
+    q, k [T, G * dk], v [T, H * dv], z [T, H * dk], beta [T, H] (logits): 32-bit rows, possibly column ranges of a
+    wider matrix. state: [slots, >= H * dk * dv] 32-bit, the matrix state first in each slot. out [T, H * dv] 32-bit."""
+    T = out.shape[0]
+    R = cu_q.shape[0] - 1
+    ldq, ldk, ldv, ldz = (_rows32(q, "q", T, G * dk), _rows32(k, "k", T, G * dk), _rows32(v, "v", T, H * dv),
+                          _rows32(z, "z", T, H * dk))
+    ldb = _rows32(beta, "beta", T, H) if beta is not None else 0
+    _need(coef, "coef", torch.float32, (H,)); _need(slots, "slots", torch.int32); _need(cu_q, "cu_q", torch.int32)
+    _need(out, "out", torch.float32, (T, H * dv))
+    if not state.is_cuda or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < H * dk * dv:
+        raise KernelError("state: must be 32-bit [slots, >= H * dk * dv] with contiguous rows")
+    _call(_lib().bl_recurrent_scan, rule, _p(q), ldq, _p(k), ldk, _p(v), ldv, _p(z), ldz, _p(beta), ldb, _p(coef),
+          ctypes.c_float(z_sign), ctypes.c_float(q_scale), _p(state), ctypes.c_longlong(state.stride(0)), _p(slots), _p(cu_q), R,
+          _p(out), H, G, dk, dv, _stream())
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], gate_kind: int, eps: float,
+                   out: torch.Tensor, H: int, dv: int) -> None:
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * g(gate[t, h]), g = sigmoid or silu (gate None: 1)."""
+    T = o.shape[0]
+    _need(o, "o", torch.float32, (T, H * dv)); _need(weight, "weight", None, (dv,)); _need(out, "out", None, (T, H * dv))
+    ld = _rows32(gate, "gate", T, H * dv) if gate is not None else 0
+    _call(_lib().bl_head_norm_gate, _p(o), _p(weight), _dt(weight), _p(gate), ld, gate_kind, _p(out), _dt(out), T, H, dv,
+          ctypes.c_float(eps), _stream())
+
+
+def conv_silu_unit(x: torch.Tensor, taps: torch.Tensor, tail: torch.Tensor, slots: torch.Tensor, tok_req: torch.Tensor,
+                   cu_q: torch.Tensor, out: torch.Tensor, unit_heads: int, scaled_heads: int, dk: int, q_scale: float,
+                   unit_eps: float) -> None:
+    """out = silu(short causal convolution of x over a request's tokens, per channel), then the first `unit_heads` heads
+    of dk columns made unit vectors (the first `scaled_heads` times q_scale). x: 32-bit rows [T, >= C]; taps [C, n]
+    32-bit (the last column is the current token's); tail: [slots, >= (n - 1) * C] 32-bit rows (a column range of the
+    state slots), each slot holding its request's last n - 1 inputs, oldest first."""
+    T, C = out.shape
+    n_taps = taps.shape[1]
+    ld = _rows32(x, "x", T, C)
+    _need(taps, "taps", torch.float32, (C, n_taps)); _need(out, "out", torch.float32)
+    _need(slots, "slots", torch.int32); _need(tok_req, "tok_req", torch.int32, (T,)); _need(cu_q, "cu_q", torch.int32)
+    if not tail.is_cuda or tail.dtype != torch.float32 or tail.stride(1) != 1 or tail.shape[1] < (n_taps - 1) * C:
+        raise KernelError("tail: must be 32-bit [slots, >= (taps - 1) * C] with contiguous rows")
+    _call(_lib().bl_conv_silu_unit, _p(x), ld, _p(taps), n_taps, _p(tail), ctypes.c_longlong(tail.stride(0)), _p(slots),
+          _p(tok_req), _p(cu_q), _p(out), T, C, unit_heads, scaled_heads, dk, ctypes.c_float(q_scale), ctypes.c_float(unit_eps),
+          _stream())
+
+
+def conv_tail_update(x: torch.Tensor, n_taps: int, tail: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, C: int) -> None:
+    """After `conv_silu_unit`: every request with tokens in this step keeps its last n_taps - 1 inputs in its slot."""
+    ld = _rows32(x, "x", x.shape[0], C)
+    _need(slots, "slots", torch.int32); _need(cu_q, "cu_q", torch.int32)
+    _call(_lib().bl_conv_tail_update, _p(x), ld, n_taps, _p(tail), ctypes.c_longlong(tail.stride(0)), _p(slots), _p(cu_q),
+          cu_q.shape[0] - 1, C, _stream())
+
+
+def linear_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int, fast: bool = True) -> None:
+    """out = act(x @ w.T), the activation evaluated in 32-bit on the product's 32-bit sums."""
+    M = x.shape[0]
+    N = w.shape[0]
+    _need(out, "out", None, (M, N))
+    if out.dtype == torch.float32:
+        gemm(x, w, out, None, EPI_NONE, fast=fast)
+        activation(out, out, act)
+        return
+    sums = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    gemm(x, w, sums, None, EPI_NONE, fast=fast)
+    activation(sums, out, act)

@@ -1,13 +1,17 @@
 from .base import Part, StepContext, StepPlan, to_device_matrix, to_device_vector
 from .linear import linear
-from .norm import RMSNorm
+from .norm import RMSNorm, LayerNorm
 from .rotary import RotaryTable
-from .attention import Mixer, GQAAttention
-from .feedforward import FeedForward, SwiGLU
-from .block import PreNormBlock
+from .attention import Mixer, GQAAttention, GatedSinkAttention
+from .recurrent import GatedLinearAttention, ChannelDeltaRule
+from .feedforward import FeedForward, SwiGLU, DenseMLP
+from .block import PreNormBlock, GatedSandwichBlock, ResidualGate
+from .depth import DepthWeightedAverage
 from .embedding import Embedding, OutputHead
 from .model import DecoderModel, LayerCall
 
 __all__ = ["Part", "StepContext", "StepPlan", "to_device_matrix", "to_device_vector", "linear", "RMSNorm",
-           "RotaryTable", "Mixer", "GQAAttention", "FeedForward", "SwiGLU", "PreNormBlock",
+           "LayerNorm", "RotaryTable", "Mixer", "GQAAttention", "GatedSinkAttention", "GatedLinearAttention",
+           "ChannelDeltaRule", "FeedForward", "SwiGLU", "DenseMLP", "PreNormBlock", "GatedSandwichBlock", "ResidualGate",
+           "DepthWeightedAverage",
            "Embedding", "OutputHead", "DecoderModel", "LayerCall"]

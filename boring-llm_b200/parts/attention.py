@@ -9,7 +9,7 @@ import torch
 
 from ..cache import PagedKVSpec
 from ..kernels import ops
-from ..weights import TensorSpec, MATRIX, BIAS
+from ..weights import TensorSpec, MATRIX, BIAS, NORM
 from .base import PendingNormRows, Part, StepPlan, to_device_matrix, to_device_vector
 from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
 from .norm import RMSNorm
@@ -90,6 +90,13 @@ class Mixer(Part):
         """Optional: run `norm` and this mixer on the residual stream `x` in fused kernels and return True,
         or return False to be called with the normed rows as usual."""
         return False
+
+    def mix(self, ctx, h, out, cache_layer: Optional[int], write_cache: bool = True) -> None:
+        """Writes the result into the 32-bit `out` [T, dim] instead of adding it to a stream (for arrangements that
+        treat a sublayer's result before the residual sum). Mixers whose last product can write as well as add
+        override this; the default clears `out` and adds."""
+        out.zero_()
+        self.forward(ctx, h, out, cache_layer, write_cache)
 
 
 class GQAAttention(Mixer):
@@ -243,3 +250,97 @@ class GQAAttention(Mixer):
             n_splits = max(1, min(-(-longest // 64), resident // (n * groups), DECODE_MAX_SPLITS))
             ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out,
                                  self.H, self.window, self.scale)
+
+
+class GatedSinkAttention(Mixer):
+    """Causal grouped-query attention over the paged cache with the options of newer designs, each a constructor
+    argument:
+
+    * `v_head_dim`: values of another head size than queries and keys;
+    * `qk_norm="whole"`: an RMS norm over a token's whole q projection, and one over its whole k projection (all heads
+      at once, plain weights), before the rotation (None: no norm);
+    * `rotary`: any `RotaryTable` (pairs "halves" or "interleaved", partial rotation);
+    * `window`: position i sees j with 0 <= i - j < window (0: every j <= i);
+    * `sink=True`: a learned score per head whose exponential joins the softmax's denominator once, unscaled, with no
+      key and no value;
+    * `out_gate=True`: head h's output is multiplied by sigmoid(h . Wg^T)[h], one number per token and head, read from
+      the same rows as the projections.
+
+    q, k, v and the gate's logits are ONE joined product with 32-bit sums; norm, rotation and the cache write are one
+    kernel; scores, softmax and the sink are 32-bit.
+    """
+    graph_safe = True
+
+    def __init__(self, dim: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: Optional[int],
+                 rotary: Optional[RotaryTable], names: Dict[str, str], window: int = 0, scale: Optional[float] = None,
+                 qk_norm: Optional[str] = None, qk_norm_eps: float = 1e-6, sink: bool = False, out_gate: bool = False):
+        super().__init__(names)
+        if n_heads % n_kv_heads != 0:
+            raise ValueError(f"{n_heads} query heads cannot share {n_kv_heads} key/value heads")
+        if qk_norm not in (None, "whole"):
+            raise ValueError(f"qk_norm must be None or 'whole', got {qk_norm!r}")
+        self.dim, self.H, self.KV, self.dk = dim, n_heads, n_kv_heads, head_dim
+        self.dv = head_dim if v_head_dim is None else int(v_head_dim)
+        self.rotary = rotary if rotary is not None else RotaryTable(head_dim, 10000.0, n_rot=0)
+        self.window = int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.qk_norm, self.qk_norm_eps, self.has_sink, self.out_gate = qk_norm, float(qk_norm_eps), bool(sink), bool(out_gate)
+        self.off_k = self.H * self.dk
+        self.off_v = self.off_k + self.KV * self.dk
+        self.off_g = self.off_v + self.KV * self.dv
+        self.n_in = self.off_g + (self.H if self.out_gate else 0)
+        self.w_in = self.wo = self.q_norm = self.k_norm = self.sinks = None
+
+    def local_specs(self):
+        s = {"wq": TensorSpec((self.H * self.dk, self.dim), MATRIX), "wk": TensorSpec((self.KV * self.dk, self.dim), MATRIX),
+             "wv": TensorSpec((self.KV * self.dv, self.dim), MATRIX), "wo": TensorSpec((self.dim, self.H * self.dv), MATRIX)}
+        if self.qk_norm:
+            s["q_norm"] = TensorSpec((self.H * self.dk,), NORM)
+            s["k_norm"] = TensorSpec((self.KV * self.dk,), NORM)
+        if self.has_sink:
+            s["sink"] = TensorSpec((self.H,), BIAS)
+        if self.out_gate:
+            s["wg"] = TensorSpec((self.H, self.dim), MATRIX)
+        return s
+
+    def place(self, local, dtype, device):
+        joined = [local["wq"], local["wk"], local["wv"]] + ([local["wg"]] if self.out_gate else [])
+        self.w_in = to_device_matrix(torch.cat(joined, dim=0), dtype, device)
+        self.wo = to_device_matrix(local["wo"], dtype, device)
+        if self.qk_norm:
+            self.q_norm = to_device_vector(local["q_norm"], dtype, device)
+            self.k_norm = to_device_vector(local["k_norm"], dtype, device)
+        if self.has_sink:
+            self.sinks = to_device_vector(local["sink"], dtype, device)
+        self.rotary.to(device)
+
+    def cache_spec(self):
+        return PagedKVSpec(self.KV, self.dk, self.window, 0 if self.dv == self.dk else self.dv)
+
+    def plan_step(self, q_lens, ctx_lens, filler=None):
+        return PLAN_KEY, attention_plan(q_lens, ctx_lens, filler)
+
+    def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
+        T = h.shape[0]
+        k_cache, v_cache, table = ctx.kv(cache_layer)
+        proj = ctx.empty((T, self.n_in), torch.float32)
+        linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        q = ctx.empty((T, self.H * self.dk))
+        ops.qk_norm_rope_write(proj, self.off_k, self.off_v, self.q_norm, self.k_norm, self.qk_norm_eps, ctx.positions,
+                               ctx.tok_req, table, self.rotary.inv_freq, self.rotary.rot_half, self.rotary.pair_layout, q,
+                               k_cache if write_cache else None, v_cache if write_cache else None, self.H, self.KV,
+                               self.dk, self.dv)
+        attn = ctx.empty((T, self.H * self.dv))
+        gate = proj[:, self.off_g:self.off_g + self.H] if self.out_gate else None
+        self.attend(ctx, q, k_cache, v_cache, table, attn, gate)
+        linear(ctx, attn, self.wo, out, None, epilogue)
+
+    def forward(self, ctx, h, residual, cache_layer, write_cache=True):
+        self._run(ctx, h, residual, cache_layer, write_cache, EPI_RESIDUAL)
+
+    def mix(self, ctx, h, out, cache_layer, write_cache=True):
+        self._run(ctx, h, out, cache_layer, write_cache, EPI_NONE)
+
+    def attend(self, ctx, q, k_cache, v_cache, table, out, gate):
+        ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out, self.H, self.window,
+                            self.scale, self.sinks, gate)

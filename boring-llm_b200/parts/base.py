@@ -160,11 +160,12 @@ class StepContext:
         return max(self.q_lens) if self.q_lens else 0
 
     def kv(self, cache_layer: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-        """(keys, values, block table) of a cache layer: pages `[pages, kv heads, page size, head size]`."""
+        """(keys, values, block table) of a cache layer: pages `[pages, kv heads, page size, head size]` (the values'
+        head size may differ from the keys')."""
         kind, gi, li = self.storage.manager.layer_location[cache_layer]
         if kind != "paged":
             raise TypeError(f"cache layer {cache_layer} holds fixed-size state, not pages")
-        return self.storage.kv[gi][li, 0], self.storage.kv[gi][li, 1], self.block_tables[gi]
+        return self.storage.k_pages[gi][li], self.storage.v_pages[gi][li], self.block_tables[gi]
 
     def state(self, cache_layer: int) -> torch.Tensor:
         """`[request slots, *shape]` of a cache layer with fixed-size state; index it with `slots`."""

@@ -3,7 +3,12 @@ from __future__ import annotations
 
 from typing import Optional
 
-from .base import Part, takes_pending_norm
+import torch
+
+from ..kernels import ops
+from ..weights import TensorSpec, MATRIX, BIAS
+from .base import Part, takes_pending_norm, to_device_matrix, to_device_vector
+from .linear import linear, EPI_BIAS, EPI_NONE
 
 
 class PreNormBlock(Part):
@@ -47,3 +52,69 @@ class PreNormBlock(Part):
             except TypeError:                    # a norm part without the option
                 pass
         return norm.forward(ctx, x)
+
+
+class ResidualGate(Part):
+    """The logits of a gate on a sublayer's result: h . W^T (+ b), one per channel of the stream, 32-bit. The sigmoid and
+    the product with the sublayer's result belong to the kernel that adds the result to the stream."""
+
+    def __init__(self, dim: int, names, bias: bool = True):
+        super().__init__(names)
+        self.dim, self.has_bias = dim, bool(bias)
+        self.weight = self.bias = None
+
+    def local_specs(self):
+        s = {"weight": TensorSpec((self.dim, self.dim), MATRIX)}
+        if self.has_bias:
+            s["bias"] = TensorSpec((self.dim,), BIAS)
+        return s
+
+    def logits(self, ctx, h):
+        out = ctx.empty((h.shape[0], self.dim), torch.float32)
+        linear(ctx, h, self.weight, out, self.bias, EPI_BIAS if self.has_bias else EPI_NONE)
+        return out
+
+
+class GatedSandwichBlock(Part):
+    """Norms on both sides of each sublayer and a gate on its result:
+
+        x += post1(mixer(h) * sigmoid(gate1(h))),  h = pre1(x)
+        x += post2(ffn(h)   * sigmoid(gate2(h))),  h = pre2(x)      (a block without a feed-forward has only the first)
+
+    The gates read what the sublayer reads and act before the norm behind it. `post*` are `LayerNorm` parts (the gate,
+    that norm and the residual sum are one kernel); a gate may be None. The sublayers write their results instead of
+    adding them (`Mixer.mix`, `FeedForward.apply`)."""
+
+    def __init__(self, mixer_norm, mixer, mixer_post_norm, mixer_gate, ffn_norm=None, ffn=None, ffn_post_norm=None, ffn_gate=None):
+        super().__init__()
+        self.mixer_norm, self.mixer, self.mixer_post_norm, self.mixer_gate = mixer_norm, mixer, mixer_post_norm, mixer_gate
+        self.ffn_norm, self.ffn, self.ffn_post_norm, self.ffn_gate = ffn_norm, ffn, ffn_post_norm, ffn_gate
+        if ffn is not None and (ffn_norm is None or ffn_post_norm is None):
+            raise ValueError("GatedSandwichBlock: a feed-forward needs the norms on both of its sides")
+
+    def children(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.mixer_gate, self.ffn_norm, self.ffn,
+                                 self.ffn_post_norm, self.ffn_gate) if p is not None)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    @property
+    def graph_safe(self) -> bool:
+        return bool(getattr(self.mixer, "graph_safe", False) and (self.ffn is None or getattr(self.ffn, "graph_safe", False)))
+
+    def forward(self, ctx, x, cache_layer: Optional[int], write_cache: bool = True) -> None:
+        ctx.next_norm = None                     # no product of this block may begin a norm for its successor
+        h = self.mixer_norm.forward(ctx, x)
+        sub = ctx.empty(tuple(x.shape), torch.float32)
+        self.mixer.mix(ctx, h, sub, cache_layer, write_cache)
+        self._add(ctx, x, sub, h, self.mixer_gate, self.mixer_post_norm)
+        if self.ffn is not None:
+            h = self.ffn_norm.forward(ctx, x)
+            self.ffn.apply(ctx, h, sub)
+            self._add(ctx, x, sub, h, self.ffn_gate, self.ffn_post_norm)
+
+    @staticmethod
+    def _add(ctx, x, sub, h, gate, post):
+        g = gate.logits(ctx, h) if gate is not None else None
+        ops.gated_norm_residual(x, sub, g, post.weight, getattr(post, "bias", None), post.eps)

@@ -29,8 +29,8 @@ class Embedding(Part):
     def place(self, local, dtype, device):
         self.table = to_device_matrix(local["table"], dtype, device)
 
-    def forward(self, ctx) -> torch.Tensor:
-        x = ctx.empty((ctx.T, self.dim), torch.float32)
+    def forward(self, ctx, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = ctx.empty((ctx.T, self.dim), torch.float32) if out is None else out
         ops.embed(self.table, ctx.token_ids, x)
         return x
 

@@ -8,7 +8,7 @@ import torch
 from ..kernels import ops
 from ..weights import TensorSpec, MATRIX
 from .base import Part, to_device_matrix
-from .linear import linear, EPI_RESIDUAL, EPI_SWIGLU
+from .linear import linear, EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU
 
 
 FF_FUSED_MAX_ROWS = 16    # more rows: a separate norm and the tcgen05 product are faster (measured: 6% of a step at 24 and 32 rows)
@@ -26,6 +26,40 @@ class FeedForward(Part):
         """Optional: run `norm` and this feed-forward on the residual stream `x` in fused kernels and return
         True, or return False to be called with the normed rows as usual."""
         return False
+
+    def apply(self, ctx, h, out) -> None:
+        """Writes the result into the 32-bit `out` [T, dim] instead of adding it to a stream (for arrangements
+        that treat a sublayer's result before the residual sum: gates, norms behind the sublayer)."""
+        out.zero_()
+        self.forward(ctx, h, out)
+
+
+class DenseMLP(FeedForward):
+    """down(act(up(h))), no biases, no gate branch; `activation`: "gelu" (exact, erf), "gelu_tanh" or "silu",
+    evaluated in 32-bit on the up product's 32-bit sums."""
+    graph_safe = True
+    ACTIVATIONS = {"silu": ops.ACT_SILU, "gelu": ops.ACT_GELU_ERF, "gelu_tanh": ops.ACT_GELU_TANH}
+
+    def __init__(self, dim: int, hidden: int, names: Dict[str, str], activation: str = "gelu"):
+        super().__init__(names)
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"DenseMLP: activation must be one of {sorted(self.ACTIVATIONS)}, got {activation!r}")
+        self.dim, self.hidden, self.activation = dim, hidden, activation
+        self.w_up = self.w_down = None
+
+    def local_specs(self):
+        return {"w_up": TensorSpec((self.hidden, self.dim), MATRIX), "w_down": TensorSpec((self.dim, self.hidden), MATRIX)}
+
+    def _run(self, ctx, h, out, epilogue):
+        act = ctx.empty((h.shape[0], self.hidden))
+        ops.linear_act(h, self.w_up, act, self.ACTIVATIONS[self.activation], fast=ctx.fast)
+        linear(ctx, act, self.w_down, out, None, epilogue)
+
+    def forward(self, ctx, h, residual):
+        self._run(ctx, h, residual, EPI_RESIDUAL)
+
+    def apply(self, ctx, h, out):
+        self._run(ctx, h, out, EPI_NONE)
 
 
 class SwiGLU(FeedForward):

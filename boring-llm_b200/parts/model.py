@@ -28,9 +28,14 @@ class DecoderModel(Part):
     """
 
     def __init__(self, embedding, blocks: Sequence[Part], final_norm, head,
-                 schedule: Optional[Sequence[LayerCall]] = None, ignorable_tensors: Sequence[str] = ()):
+                 schedule: Optional[Sequence[LayerCall]] = None, ignorable_tensors: Sequence[str] = (),
+                 depth_mix: Optional[Sequence[Part]] = None):
+        """`depth_mix`: one part per entry of the run order (`parts.depth.DepthWeightedAverage`); entry i's part turns the
+        streams X_0 .. X_(i+1) (the embedding rows and what each entry so far left) into what the next entry, or the
+        final norm, reads. Without it every entry reads what the one before left."""
         super().__init__()
         self.embedding, self.blocks, self.final_norm, self.head = embedding, list(blocks), final_norm, head
+        self.depth_mix = list(depth_mix) if depth_mix is not None else None
         self.schedule: List[LayerCall] = list(schedule) if schedule is not None else [
             LayerCall(i, i if b.cache_spec() is not None else None) for i, b in enumerate(self.blocks)]
         self.ignorable_tensors = tuple(ignorable_tensors)
@@ -45,9 +50,11 @@ class DecoderModel(Part):
                     written.add(call.cache)
                 elif call.cache not in written:
                     raise ValueError(f"an entry reads cache layer {call.cache} before any entry writes it")
+        if self.depth_mix is not None and len(self.depth_mix) != len(self.schedule):
+            raise ValueError(f"{len(self.depth_mix)} depth-mix parts for {len(self.schedule)} entries of the run order")
 
     def children(self):
-        return (self.embedding, *self.blocks, self.final_norm, self.head)
+        return (self.embedding, *self.blocks, *(self.depth_mix or ()), self.final_norm, self.head)
 
     @property
     def vocab_size(self) -> int:
@@ -74,6 +81,9 @@ class DecoderModel(Part):
     def forward(self, ctx) -> torch.Tensor:
         """Runs the tokens of `ctx` through every layer and returns 32-bit logits at `ctx.logit_rows`."""
         ctx.memo.clear()                        # a context may be run again (before a capture, at a replay's capture): nothing is carried over
+        if self.depth_mix is not None:
+            x = self._forward_depth_mixed(ctx)
+            return self._logits(ctx, x)
         x = self.embedding.forward(ctx)
         for i, call in enumerate(self.schedule):
             # the norm that reads the stream after this block: the next block's first (the final norm reads a few rows only)
@@ -82,6 +92,24 @@ class DecoderModel(Part):
             ctx.norm_after_block = getattr(after, "mixer_norm", None) if takes_pending_norm(reader, x.shape[0]) else None
             self.blocks[call.block].forward(ctx, x, call.cache, call.write_cache)
         ctx.norm_after_block = None
+        return self._logits(ctx, x)
+
+    def _forward_depth_mixed(self, ctx) -> torch.Tensor:
+        """All streams live in one buffer [entries + 2, T, dim]: stream 0 the embedding rows; entry i works in place in
+        stream i + 1, which its predecessor's mix has filled with what it reads, and leaves X_(i+1) there; its own mix
+        writes stream i + 2. Nothing is copied but the embedding rows, once."""
+        n = len(self.schedule)
+        streams = ctx.empty((n + 2, ctx.T, self.embedding.dim), torch.float32)
+        self.embedding.forward(ctx, out=streams[0])
+        streams[1].copy_(streams[0])
+        ctx.norm_after_block = None
+        for i, call in enumerate(self.schedule):
+            self.blocks[call.block].forward(ctx, streams[i + 1], call.cache, call.write_cache)
+            self.depth_mix[i].forward(ctx, streams, streams[i + 2])
+        ctx.memo["streams"] = streams            # for whoever wants to look at the stream after each entry (tests)
+        return streams[n + 1]
+
+    def _logits(self, ctx, x) -> torch.Tensor:
         if ctx.logit_rows.shape[0] == 0:
             return ctx.empty((0, self.vocab_size), torch.float32)
         fused = getattr(self.head, "forward_fused_norm", None)

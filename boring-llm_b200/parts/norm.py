@@ -6,7 +6,7 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import ops
-from ..weights import TensorSpec, NORM
+from ..weights import TensorSpec, NORM, BIAS
 from .base import Part
 
 
@@ -32,4 +32,28 @@ class RMSNorm(Part):
         rows = x.shape[0] if row_idx is None else row_idx.shape[0]
         out = ctx.empty((rows, self.dim))
         ops.rmsnorm(x, self.weight, self.eps, out, row_idx)
+        return out
+
+
+class LayerNorm(Part):
+    """y = (x - mean) / sqrt(var + eps) * weight + bias over each row, var the mean of the squared deviations; statistics
+    in 32-bit. Input: the 32-bit residual stream (or any 32-bit rows); output: the engine's activation dtype.
+    `bias=False`: no bias tensor."""
+
+    def __init__(self, dim: int, eps: float, names: Dict[str, str], bias: bool = True):
+        super().__init__(names)
+        self.dim, self.eps, self.has_bias = dim, float(eps), bool(bias)
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def local_specs(self):
+        s = {"weight": TensorSpec((self.dim,), NORM)}
+        if self.has_bias:
+            s["bias"] = TensorSpec((self.dim,), BIAS)
+        return s
+
+    def forward(self, ctx, x: torch.Tensor, row_idx: Optional[torch.Tensor] = None, pending_ok: bool = False):
+        rows = x.shape[0] if row_idx is None else row_idx.shape[0]
+        out = ctx.empty((rows, self.dim))
+        ops.layernorm(x, self.weight, self.bias, self.eps, out, row_idx)
         return out

@@ -1,0 +1,172 @@
+"""Mixers that carry a matrix state per head from token to token instead of caching keys and values.
+
+Each request owns a state slot (`cache.StateSpec`); a step's kernels walk the tokens of every request in order from
+the state the step before left, prompts' portions and single decoded tokens alike, and are pure device work (the
+batch's structure comes from `ctx.cu_q` and `ctx.slots`), so steps with these mixers can be captured and replayed.
+State, decays, gates and every sum of the recurrences are 32-bit in both engine dtypes.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..cache import StateSpec
+from ..kernels import ops
+from ..weights import TensorSpec, MATRIX, BIAS, NORM
+from .attention import Mixer
+from .base import to_device_matrix, to_device_vector
+from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
+
+
+def _rank(t_a: torch.Tensor, t_b: torch.Tensor, what: str) -> int:
+    """The inner size of a product in two factors, read from the tensors: t_a [r, dim], t_b [out, r]."""
+    if t_a.shape[0] != t_b.shape[1]:
+        raise ValueError(f"{what}: the first factor has {t_a.shape[0]} rows, the second {t_b.shape[1]} columns")
+    return int(t_a.shape[0])
+
+
+class _StateMixer(Mixer):
+    graph_safe = True
+
+    def forward(self, ctx, h, residual, cache_layer, write_cache=True):
+        self._run(ctx, h, residual, cache_layer, write_cache, EPI_RESIDUAL)
+
+    def mix(self, ctx, h, out, cache_layer, write_cache=True):
+        self._run(ctx, h, out, cache_layer, write_cache, EPI_NONE)
+
+    @staticmethod
+    def _check(write_cache):
+        if not write_cache:
+            raise ValueError("a mixer with recurrent state cannot read the state another entry of the run order wrote")
+
+
+class GatedLinearAttention(_StateMixer):
+    """Per head, with a decay per key channel:
+
+        S_t = diag(a_t) S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t,   a_t = sigmoid(z_t)^(1 / tau),
+        z = (h A1^T) A2^T + b,   q = (h Wq^T) / sqrt(key_dim)
+
+    then each head's o is RMS-normed over its value channels (one plain weight shared by the heads), the heads are
+    joined, multiplied by silu(h Wg^T) and projected by Wo. `decay_rank` is the inner size of the decay's two factors
+    (None: taken from the tensors when they are loaded)."""
+
+    def __init__(self, dim: int, n_heads: int, key_dim: int, value_dim: int, tau: float, norm_eps: float,
+                 names: Dict[str, str], decay_rank: Optional[int] = None):
+        super().__init__(names)
+        self.dim, self.H, self.dk, self.dv = dim, n_heads, key_dim, value_dim
+        self.tau, self.eps, self.rank = float(tau), float(norm_eps), decay_rank
+        self.off_k = self.H * self.dk
+        self.off_v = 2 * self.H * self.dk
+        self.off_g = self.off_v + self.H * self.dv
+        self.off_a = self.off_g + self.H * self.dv
+        self.w_in = self.wo = self.a2 = self.a2_bias = self.norm = self.coef = None
+
+    def local_specs(self):
+        r = -1 if self.rank is None else self.rank
+        return {"wq": TensorSpec((self.H * self.dk, self.dim), MATRIX), "wk": TensorSpec((self.H * self.dk, self.dim), MATRIX),
+                "wv": TensorSpec((self.H * self.dv, self.dim), MATRIX), "wg": TensorSpec((self.H * self.dv, self.dim), MATRIX),
+                "wo": TensorSpec((self.dim, self.H * self.dv), MATRIX), "norm": TensorSpec((self.dv,), NORM),
+                "a1": TensorSpec((r, self.dim), MATRIX), "a2": TensorSpec((self.H * self.dk, r), MATRIX),
+                "a2_bias": TensorSpec((self.H * self.dk,), BIAS)}
+
+    def place(self, local, dtype, device):
+        self.rank = _rank(local["a1"], local["a2"], "the decay's factors")
+        self.w_in = to_device_matrix(torch.cat([local[n] for n in ("wq", "wk", "wv", "wg", "a1")], dim=0), dtype, device)
+        self.wo = to_device_matrix(local["wo"], dtype, device)
+        self.a2 = to_device_matrix(local["a2"], dtype, device)
+        self.a2_bias = to_device_vector(local["a2_bias"], dtype, device)
+        self.norm = to_device_vector(local["norm"], dtype, device)
+        self.coef = torch.full((self.H,), 1.0 / self.tau, dtype=torch.float32, device=device)
+
+    def cache_spec(self):
+        return StateSpec((self.H * self.dk * self.dv,), "float32")
+
+    def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
+        self._check(write_cache)
+        T, H, dk, dv = h.shape[0], self.H, self.dk, self.dv
+        proj = ctx.empty((T, self.off_a + self.rank), torch.float32)
+        linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        z = ctx.empty((T, H * dk), torch.float32)
+        ops.gemm_plain(proj[:, self.off_a:], self.a2, z, self.a2_bias, EPI_BIAS)
+        o = ctx.empty((T, H * dv), torch.float32)
+        ops.recurrent_scan(ops.RULE_GLA, proj[:, :self.off_k], proj[:, self.off_k:self.off_v], proj[:, self.off_v:self.off_g],
+                           z, None, self.coef, -1.0, dk ** -0.5, ctx.state(cache_layer), ctx.slots, ctx.cu_q, o, H, H, dk, dv)
+        y = ctx.empty((T, H * dv))
+        ops.head_norm_gate(o, self.norm, proj[:, self.off_g:self.off_a], ops.GATE_SILU, self.eps, y, H, dv)
+        linear(ctx, y, self.wo, out, None, epilogue)
+
+
+class ChannelDeltaRule(_StateMixer):
+    """The gated delta rule with a decay per head AND key channel. q, k (`n_qk_heads` heads of `key_dim`; head h of the
+    `n_heads` value heads reads q/k head h // (n_heads / n_qk_heads)) and v pass a short causal convolution over time
+    per channel and a SiLU; q and k become unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q also times
+    1 / sqrt(key_dim). Per head
+
+        S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q       (the read-out sees the token's write)
+        g = exp(-exp(A_log[head]) * softplus((h A1^T) A2^T + dt_bias)),   beta = sigmoid(h Wb^T)
+
+    then o is divided by its root mean square over the value channels, times a plain weight shared by the heads, times
+    sigmoid((h G1^T) G2^T), and projected by Wo. The state slot holds S and the convolution's last taps - 1 inputs."""
+    UNIT_EPS = 1e-6
+
+    def __init__(self, dim: int, n_heads: int, n_qk_heads: int, key_dim: int, value_dim: int, conv_taps: int,
+                 norm_eps: float, names: Dict[str, str], decay_rank: Optional[int] = None, gate_rank: Optional[int] = None):
+        super().__init__(names)
+        if n_heads % n_qk_heads != 0:
+            raise ValueError(f"{n_heads} value heads cannot share {n_qk_heads} query/key heads")
+        self.dim, self.H, self.G, self.dk, self.dv = dim, n_heads, n_qk_heads, key_dim, value_dim
+        self.taps, self.eps = int(conv_taps), float(norm_eps)
+        self.decay_rank, self.gate_rank = decay_rank, gate_rank
+        self.C = 2 * self.G * self.dk + self.H * self.dv          # channels that pass the convolution: q | k | v
+        self.off_b = self.C
+        self.off_a = self.off_b + self.H
+        self.w_in = self.wo = self.a2 = self.dt_bias = self.g2 = self.norm = self.coef = self.conv = None
+
+    def local_specs(self):
+        ra = -1 if self.decay_rank is None else self.decay_rank
+        rg = -1 if self.gate_rank is None else self.gate_rank
+        G, H, dk, dv, d = self.G, self.H, self.dk, self.dv, self.dim
+        return {"wq": TensorSpec((G * dk, d), MATRIX), "q_conv": TensorSpec((G * dk, self.taps), MATRIX),
+                "wk": TensorSpec((G * dk, d), MATRIX), "k_conv": TensorSpec((G * dk, self.taps), MATRIX),
+                "wv": TensorSpec((H * dv, d), MATRIX), "v_conv": TensorSpec((H * dv, self.taps), MATRIX),
+                "wb": TensorSpec((H, d), MATRIX), "a_log": TensorSpec((H,), BIAS), "norm": TensorSpec((dv,), NORM),
+                "a1": TensorSpec((ra, d), MATRIX), "a2": TensorSpec((H * dk, ra), MATRIX), "dt_bias": TensorSpec((H * dk,), BIAS),
+                "g1": TensorSpec((rg, d), MATRIX), "g2": TensorSpec((H * dv, rg), MATRIX), "wo": TensorSpec((d, H * dv), MATRIX)}
+
+    def place(self, local, dtype, device):
+        self.decay_rank = _rank(local["a1"], local["a2"], "the decay's factors")
+        self.gate_rank = _rank(local["g1"], local["g2"], "the output gate's factors")
+        self.off_g = self.off_a + self.decay_rank
+        self.w_in = to_device_matrix(torch.cat([local[n] for n in ("wq", "wk", "wv", "wb", "a1", "g1")], dim=0), dtype, device)
+        self.wo = to_device_matrix(local["wo"], dtype, device)
+        self.a2 = to_device_matrix(local["a2"], dtype, device)
+        self.g2 = to_device_matrix(local["g2"], dtype, device)
+        self.dt_bias = to_device_vector(local["dt_bias"], dtype, device)
+        self.norm = to_device_vector(local["norm"], dtype, device)
+        self.conv = torch.cat([local[n].to(torch.float32) for n in ("q_conv", "k_conv", "v_conv")], dim=0).to(device).contiguous()
+        self.coef = torch.exp(local["a_log"].to(torch.float32)).to(device).contiguous()
+
+    def cache_spec(self):
+        return StateSpec((self.H * self.dk * self.dv + (self.taps - 1) * self.C,), "float32")
+
+    def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
+        self._check(write_cache)
+        T, H, G, dk, dv, C = h.shape[0], self.H, self.G, self.dk, self.dv, self.C
+        proj = ctx.empty((T, self.off_g + self.gate_rank), torch.float32)
+        linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        state = ctx.state(cache_layer)
+        tail = state[:, H * dk * dv:]
+        qkv = ctx.empty((T, C), torch.float32)
+        ops.conv_silu_unit(proj, self.conv, tail, ctx.slots, ctx.tok_req, ctx.cu_q, qkv, 2 * G, G, dk, dk ** -0.5, self.UNIT_EPS)
+        ops.conv_tail_update(proj, self.taps, tail, ctx.slots, ctx.cu_q, C)
+        z = ctx.empty((T, H * dk), torch.float32)
+        ops.gemm_plain(proj[:, self.off_a:self.off_g], self.a2, z, self.dt_bias, EPI_BIAS)
+        glog = ctx.empty((T, H * dv), torch.float32)
+        ops.gemm_plain(proj[:, self.off_g:], self.g2, glog, None, EPI_NONE)
+        o = ctx.empty((T, H * dv), torch.float32)
+        ops.recurrent_scan(ops.RULE_DELTA, qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], z,
+                           proj[:, self.off_b:self.off_a], self.coef, 1.0, 1.0, state, ctx.slots, ctx.cu_q, o, H, G, dk, dv)
+        y = ctx.empty((T, H * dv))
+        ops.head_norm_gate(o, self.norm, glog, ops.GATE_SIGMOID, self.eps, y, H, dv)
+        linear(ctx, y, self.wo, out, None, epilogue)

@@ -22,8 +22,14 @@ MATRIX, NORM, BIAS, INT_TABLE = "matrix", "norm", "bias", "int_table"
 
 @dataclass(frozen=True)
 class TensorSpec:
+    """`shape`: a dimension of -1 is a size that only the checkpoint gives (the inner size of a product in two
+    factors); the part that owns the tensor reads it when the tensor is placed."""
     shape: Tuple[int, ...]
     kind: str = MATRIX          # MATRIX | NORM | BIAS | INT_TABLE
+
+
+def shape_matches(shape, spec_shape) -> bool:
+    return len(shape) == len(spec_shape) and all(w == -1 or int(s) == int(w) for s, w in zip(shape, spec_shape))
 
 
 class WeightsError(ValueError):
@@ -65,7 +71,7 @@ def load_checkpoint(model_dir: str, expected: Dict[str, TensorSpec],
         if name not in files:
             continue
         dtype, shape = files[name].info(name)
-        if tuple(shape) != tuple(spec.shape):
+        if not shape_matches(tuple(shape), tuple(spec.shape)):
             wrong_shape.append(f"{name}: file has {list(shape)}, configuration needs {list(spec.shape)}")
             continue
         try:

@@ -121,6 +121,9 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype = t
     """The tensor `name` of the random model `seed`: matrices and biases N(0, std), norm weights 1 + N(0, std),
     integer tables uniform in [0, vocab_size), stored as `dtype` (integer tables as int32)."""
     device = torch.device(device)
+    if any(int(d) < 0 for d in spec.shape):
+        raise ValueError(f"tensor {name}: a size that only a checkpoint gives ({tuple(spec.shape)}) must be set in the "
+                         f"configuration before random weights can be made")
     n = 1
     for d in spec.shape:
         n *= int(d)
