@@ -5,6 +5,7 @@ of 512 beside 63 decoding requests), for the Qwen2.5-0.5B layer sizes with rando
 its roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--sizes 0.5b|3b|7b] [--layers L]
+    python bench.py --design fezopel [--sizes 0.5b|3b] [--layers L]     # another design beside Qwen2 at equal sizes (its own JSON line)
 
 One JSON line on standard output. A "step" is one decode step of the whole batch. Requests are real ones: random
 prompts admitted by the scheduler, prefilled in portions through the engine, then decoded; the model comes from the
@@ -335,6 +336,104 @@ def cpu_baseline(sizes):
     return 64 / (time.perf_counter() - t0)
 
 
+# ---- another design beside the dense Qwen2 decoder at equal sizes ---------------------------------------------------
+FEZOPEL_WINDOW = 1024
+FEZOPEL_PATTERN = ("attention", "gla", "gla", "channel_delta")     # repeated over the layers
+
+
+def fezopel_config(sizes, n_layers):
+    """A Fezopel model with the width, heads, head size, feed-forward size, layers and vocabulary of a Qwen2.5 size: every
+    layer has the dense feed-forward; the recurrent mixers have half the heads with values twice as wide, so that each
+    mixer's output projection has the attention's shape."""
+    import boring_llm_b200 as b
+    s = SIZES[sizes]
+    d, H, KV, dh, F, V = (s[k] for k in ("hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
+                                         "intermediate_size", "vocab_size"))
+    Hr = H // 2
+    mixers = {
+        "attention": {"heads": H, "kv_heads": KV, "dim": dh, "vdim": dh, "mask": {"size": FEZOPEL_WINDOW},
+                      "rot": {"base": 1000000.0, "dims": dh}, "scale": dh ** -0.5},
+        "gla": {"heads": Hr, "dim": dh, "vdim": 2 * dh, "tau": 16.0, "rank": 16},
+        "channel_delta": {"heads": Hr, "kv_heads": Hr, "dim": dh, "vdim": 2 * dh, "conv": 4, "rank": 32, "gate_rank": 32},
+    }
+    layers = [{"type": t, "mixer": mixers[t], "mlp": {"kind": "dense", "ff": F}}
+              for t in (FEZOPEL_PATTERN[i % len(FEZOPEL_PATTERN)] for i in range(n_layers))]
+    return b.FezopelConfig.from_dict({"architecture": "Fezopel", "vocab": V, "width": d, "norm": {"eps": 1e-6}, "layers": layers,
+                                      "max_position_embeddings": 32768})
+
+
+def kernel_time_line(eng, entries):
+    """One step launched kernel by kernel with a time stamp between every two kernels: microseconds by kernel name
+    (each kernel's own time in place, without the overlap that dependent launches give)."""
+    from boring_llm_b200.kernels import ops
+    run = eng.runner
+    graphs, run.options.cuda_graphs = run.options.cuda_graphs, False
+    try:
+        before = {e.request_id: (run.cache.get(e.request_id).num_tokens if run.has_request(e.request_id) else 0) for e in entries}
+        run.step(entries)                                     # once untimed (first-use set-up)
+        if not run.cache.state_groups:                        # pages can be rolled back, recurrent state cannot: such a
+            for e in entries:                                 # model's second run continues behind the first
+                run.truncate(e.request_id, before[e.request_id])
+        with ops.StepTrace(run.device) as tr:
+            run.step(entries)
+        out = {}
+        for name, us in tr.durations():
+            k = out.setdefault(name[3:] if name.startswith("bl_") else name, [0, 0.0])
+            k[0] += 1
+            k[1] += us
+        return {n: [c, round(t, 1)] for n, (c, t) in sorted(out.items(), key=lambda kv: -kv[1][1])}
+    finally:
+        run.options.cuda_graphs = graphs
+
+
+def design_bench(args):
+    """Prefill and decode of the Fezopel design beside Qwen2 at equal sizes, random weights, bfloat16: one JSON line."""
+    import gc
+    import torch
+    import boring_llm_b200 as b
+    from boring_llm_b200.config import EngineOptions
+    from boring_llm_b200.engine import Engine
+    from boring_llm_b200.engine.runner import StepEntry
+    pk = peaks()
+    n_layers = args.layers or 8
+    out = {"design": "fezopel", "beside": "qwen2", "sizes": args.sizes, "layers": n_layers, "dtype": "bf16", "data": "synthetic",
+           "pattern": list(FEZOPEL_PATTERN), "window": FEZOPEL_WINDOW, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
+           "peaks": pk["source"], "models": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name in ("fezopel", "qwen2"):
+        cfg = (fezopel_config(args.sizes, n_layers) if name == "fezopel"
+               else b.Qwen2Config.from_dict({**COMMON, **SIZES[args.sizes], "num_hidden_layers": n_layers}))
+        opts = EngineOptions(dtype="bfloat16", ctx_size=CONTEXT, max_num_seqs=64, max_tokens=(CONTEXT + 16) * 64,
+                             max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk=PORTION, cuda_graphs=not args.no_graphs)
+        eng = Engine.from_random(cfg, 0, opts)
+        m = {}
+        pre_ms, pre_wall = prefill_timed(eng, [PREFILL_TOKENS])
+        pre4_ms, _ = prefill_timed(eng, [PORTION] * (PREFILL_TOKENS // PORTION))
+        m["prefill_2048"] = {"ms": round(pre_ms, 3), "tokens_per_s": round(PREFILL_TOKENS / (pre_ms / 1e3), 1)}
+        m["prefill_4x512"] = {"ms": round(pre4_ms, 3), "tokens_per_s": round(PREFILL_TOKENS / (pre4_ms / 1e3), 1)}
+        for batch in (8, 64):
+            d = measure_decode(eng, batch, min(args.steps, 32), max(3, args.warmup), value_regions=3, seed=batch)
+            m[f"decode_b{batch}"] = {"ms_per_step": round(d["ms_per_step"], 4), "tokens_per_s": round(d["tokens_per_s"], 1),
+                                     "launches_per_step": d["launches"] // max(1, min(args.steps, 32)),
+                                     "graph_replay_ms": round(d.get("graph_replay_ms", 0.0), 4)}
+        vocab = eng.runner.vocab_size
+        m["kernels_prefill_2048_us"] = kernel_time_line(eng, [StepEntry("tl", random_prompt(vocab, PREFILL_TOKENS, 1), [PREFILL_TOKENS - 1])])
+        for rid in list(eng.runner.cache.live_requests()):
+            eng.runner.free_request(rid)
+        for i in range(8):                          # eight requests at a context of 2,000, then one decode step's time line
+            eng.runner.step([StepEntry(f"d{i}", random_prompt(vocab, 2000, 50 + i), [])])
+        m["kernels_decode_b8_us"] = kernel_time_line(eng, [StepEntry(f"d{i}", [i + 1], [0]) for i in range(8)])
+        for rid in list(eng.runner.cache.live_requests()):
+            eng.runner.free_request(rid)
+        out["models"][name] = m
+        del eng
+        gc.collect(); torch.cuda.empty_cache()
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def model_figures(sizes, n_layers):
     s = SIZES[sizes]
     d, H, KV, dh, F, V = (s[k] for k in ("hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
@@ -360,6 +459,8 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "prefill4", "mixed"],
                     help="run one part only and print its figures (for profilers; not the benchmark line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--design", default="", choices=["", "fezopel"],
+                    help="measure another design beside Qwen2 at equal sizes instead of the default workload (its own JSON line)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -371,6 +472,8 @@ def main():
         return 2
     import torch
     assert torch.cuda.is_available(), "bench.py needs a GPU"
+    if args.design:
+        return design_bench(args)
     pk = peaks()
     warmup = max(3, args.warmup)
     n_layers = args.layers or SIZES[args.sizes]["num_hidden_layers"]

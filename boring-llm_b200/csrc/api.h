@@ -181,6 +181,28 @@ int bl_gemm_tc_splitk(const void* x, const void* w, const void* bias, int bias_d
                       int M, int N, int K, int epilogue, void* stream);
 int bl_gemm_tc_splitk_status(int* status);
 
+// The tensor-core attention kernels with what may follow the softmax: sinks[H] (null: none), a learned score per head
+// whose exponential joins the denominator once, unscaled, without a value (the slices of a decode row count it once, at
+// their merge); gate (null: none), 32-bit logits with rows ld_gate apart: head h of token t is multiplied by
+// sigmoid(gate[t * ld_gate + h]). Otherwise as the functions without `_tail`.
+int bl_attention_prefill_tail(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                              const int* ctx_len, const int* block_table, int max_pages, const int* tiles, int n_tiles,
+                              void* out, int H, int KV, int dh, int page_size, int window, float scale,
+                              const void* sinks, int sink_dtype, const float* gate, int ld_gate, void* stream);
+int bl_attention_prefill_tc_tail(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                 const int* ctx_len, const int* block_table, int max_pages, const int* tiles, int n_tiles,
+                                 void* out, int T, int n_pages, int H, int KV, int dh, int page_size, int window, float scale,
+                                 const void* sinks, int sink_dtype, const float* gate, int ld_gate, void* stream);
+int bl_attention_decode_tail(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                             const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
+                             int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh, int page_size,
+                             int window, float scale, const void* sinks, int sink_dtype, const float* gate, int ld_gate,
+                             void* stream);
+int bl_attention_decode_tma_tail(const void* q, const void* k_cache, const void* v_cache, int n_pages, const int* cu_q,
+                                 const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
+                                 int n_splits, void* out, int H, int KV, int dh, int page_size, int window, float scale,
+                                 int early, const void* sinks, int sink_dtype, const float* gate, int ld_gate, void* stream);
+
 // The plain product with rows of x that are `ldx` values apart (a column range of a wider matrix as the input).
 int bl_gemm_plain_ld(const void* x, int x_dtype, int ldx, const void* w, int w_dtype, const void* bias, int bias_dtype,
                      void* out, int out_dtype, int M, int N, int K, int epilogue, void* stream);

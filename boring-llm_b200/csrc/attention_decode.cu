@@ -74,6 +74,7 @@ struct Params {
     const int* cu_q; const int* ctx_len; const int* block_table; int max_pages;
     const int* reqs; int n_splits;
     int H, KV, window; float scale_log2;
+    BlAttnTail tail;              // a sink per head and a gate per (token, head), or nulls
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
@@ -408,7 +409,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 O.x += a.x * f; O.y += a.y * f; O.z += a.z * f; O.w += a.w * f;
             }
             if (n_splits == 1) {
-                const float inv = L > 0.f ? 1.0f / L : 0.f;
+                const float inv = bl_attn_tail(p.tail, M, L, (size_t)q_begin, head0 + row);
                 *reinterpret_cast<uint2*>(p.out + ((size_t)q_begin * p.H + head0 + row) * DH + d) =
                     make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
             } else {
@@ -438,7 +439,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 L += ml.y * f;
                 O.x += a.x * f; O.y += a.y * f; O.z += a.z * f; O.w += a.w * f;
             }
-            const float inv = L > 0.f ? 1.0f / L : 0.f;
+            const float inv = bl_attn_tail(p.tail, M, L, (size_t)q_begin, head0 + row);
             *reinterpret_cast<uint2*>(p.out + ((size_t)q_begin * p.H + head0 + row) * DH + d) =
                 make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
         }
@@ -536,6 +537,15 @@ extern "C" int bl_attention_decode_tma(const void* q, const void* k_cache, const
                                        const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
                                        int n_splits, void* out, int H, int KV, int dh, int page_size, int window,
                                        float scale, int early, void* stream) {
+    return bl_attention_decode_tma_tail(q, k_cache, v_cache, n_pages, cu_q, ctx_len, block_table, max_pages, reqs, n, n_splits,
+                                        out, H, KV, dh, page_size, window, scale, early, nullptr, 0, nullptr, 0, stream);
+}
+
+extern "C" int bl_attention_decode_tma_tail(const void* q, const void* k_cache, const void* v_cache, int n_pages, const int* cu_q,
+                                            const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
+                                            int n_splits, void* out, int H, int KV, int dh, int page_size, int window,
+                                            float scale, int early, const void* sinks, int sink_dtype, const float* gate,
+                                            int ld_gate, void* stream) {
     if (n <= 0) return 0;
     if (!(scale > 0.f)) BL_FAIL("%s: the scale of the scores must be positive (got %g)", WHO, (double)scale);
     if (H <= 0 || KV <= 0 || H % KV != 0) BL_FAIL("%s: %d heads cannot share %d key/value heads", WHO, H, KV);
@@ -547,6 +557,7 @@ extern "C" int bl_attention_decode_tma(const void* q, const void* k_cache, const
     p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len;
     p.block_table = block_table; p.max_pages = max_pages; p.reqs = reqs; p.n_splits = n_splits;
     p.H = H; p.KV = KV; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    p.tail = BlAttnTail{sinks, sink_dtype, gate, ld_gate};
     CUtensorMap mk, mv;
     if (bl_make_map_bf16(WHO, &mk, k_cache, (long long)n_pages * KV * PAGE, dh, PAGE, 64)) return 1;
     if (bl_make_map_bf16(WHO, &mv, v_cache, (long long)n_pages * KV * PAGE, dh, PAGE, 64)) return 1;

@@ -34,6 +34,7 @@ struct AttnParams {
     float* part_o; float* part_ml; int n_splits;
     int* counters;                // decode with slices: one per (request, head group), zero between launches
     int H, KV, window; float scale_log2;
+    BlAttnTail tail;              // a sink per head and a gate per (token, head), or nulls
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
@@ -414,7 +415,7 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             if (!valid[h]) continue;
-            const float inv = l[h] > 0.f ? 1.0f / l[h] : 0.f;
+            const float inv = bl_attn_tail(p.tail, m[h], l[h], (size_t)(q_begin + tok[h]), head[h]);
             __nv_bfloat16* op = p.out + ((size_t)(q_begin + tok[h]) * p.H + head[h]) * DH + 2 * t;
 #pragma unroll
             for (int n = 0; n < DH / 8; ++n)
@@ -469,7 +470,7 @@ attention_mma_kernel(const AttnParams p) {
             }
             const int hd = head0 + row;
             if (p.n_splits == 1) {
-                const float inv = L > 0.f ? 1.0f / L : 0.f;
+                const float inv = bl_attn_tail(p.tail, M, L, (size_t)q_tok, hd);
                 *reinterpret_cast<uint2*>(p.out + ((size_t)q_tok * p.H + hd) * DH + d) =
                     make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
             } else if (p.part_o == nullptr) {                             // the slices are the blocks of one cluster: the partial result stays here
@@ -512,7 +513,7 @@ attention_mma_kernel(const AttnParams p) {
                 L += ml[s2].y * f;
                 O.x += po[s2].x * f; O.y += po[s2].y * f; O.z += po[s2].z * f; O.w += po[s2].w * f;
             }
-            const float inv = L > 0.f ? 1.0f / L : 0.f;
+            const float inv = bl_attn_tail(p.tail, M, L, (size_t)q_tok, head0 + row);
             *reinterpret_cast<uint2*>(p.out + ((size_t)q_tok * p.H + head0 + row) * DH + d) =
                 make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
         }
@@ -536,6 +537,7 @@ attention_mma_kernel(const AttnParams p) {
     __threadfence();
     float* wts = reinterpret_cast<float*>(smem_raw);               // [rows_here][n_splits] weights 2^(m_s - M), then L per row
     float* sL = wts + 16 * p.n_splits;
+    float* sM = sL + 16;
     // One thread per (row, four dimensions). Its first PRE slices are requested before the weights are
     // worked out, so that the two round trips to L2 overlap.
     const int mine = threadIdx.x;                                  // rows_here * D4 <= 16 * 64: up to 8 items a thread
@@ -577,7 +579,7 @@ attention_mma_kernel(const AttnParams p) {
             }
             lsum += __shfl_sync(0xffffffffu, lv, 31);
         }
-        if (lane == 0) sL[row] = lsum;
+        if (lane == 0) { sL[row] = lsum; sM[row] = mx; }
     }
     __syncthreads();
     // sixteen 16-byte loads in flight, slices added in slice order
@@ -599,8 +601,7 @@ attention_mma_kernel(const AttnParams p) {
                 O.x += a[j].x * f; O.y += a[j].y * f; O.z += a[j].z * f; O.w += a[j].w * f;
             }
         }
-        const float L = sL[row];
-        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        const float inv = bl_attn_tail(p.tail, sM[row], sL[row], (size_t)q_tok, head0 + row);
         __nv_bfloat16* dst = p.out + ((size_t)q_tok * p.H + head0 + row) * DH + d;
         *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
     }
@@ -705,6 +706,15 @@ extern "C" int bl_attention_prefill(const void* q, const void* k_cache, const vo
                                     const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
                                     int n_tiles, void* out, int H, int KV, int dh, int page_size, int window,
                                     float scale, void* stream) {
+    return bl_attention_prefill_tail(q, k_cache, v_cache, cu_q, ctx_len, block_table, max_pages, tiles, n_tiles, out, H, KV, dh,
+                                     page_size, window, scale, nullptr, 0, nullptr, 0, stream);
+}
+
+extern "C" int bl_attention_prefill_tail(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                         const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
+                                         int n_tiles, void* out, int H, int KV, int dh, int page_size, int window,
+                                         float scale, const void* sinks, int sink_dtype, const float* gate, int ld_gate,
+                                         void* stream) {
     if (n_tiles <= 0) return 0;
     if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
     AttnParams p;
@@ -712,6 +722,7 @@ extern "C" int bl_attention_prefill(const void* q, const void* k_cache, const vo
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.work = tiles; p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr; p.n_splits = 1; p.H = H; p.KV = KV; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.tail = BlAttnTail{sinks, sink_dtype, gate, ld_gate};
     if ((long long)n_tiles * H > 2147483647LL) BL_FAIL("bl_attention_prefill: %d tiles x %d heads are more blocks than a launch takes", n_tiles, H);
     return dispatch<false>(dh, p, dim3(n_tiles * H, 1, 1), (cudaStream_t)stream);
 }
@@ -726,6 +737,15 @@ extern "C" int bl_attention_decode(const void* q, const void* k_cache, const voi
                                    const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
                                    int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh,
                                    int page_size, int window, float scale, void* stream) {
+    return bl_attention_decode_tail(q, k_cache, v_cache, cu_q, ctx_len, block_table, max_pages, reqs, n, n_splits, scratch,
+                                    counters, out, H, KV, dh, page_size, window, scale, nullptr, 0, nullptr, 0, stream);
+}
+
+extern "C" int bl_attention_decode_tail(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                        const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
+                                        int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh,
+                                        int page_size, int window, float scale, const void* sinks, int sink_dtype,
+                                        const float* gate, int ld_gate, void* stream) {
     if (n <= 0) return 0;
     if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
     if (n_splits < 1 || n_splits > 256) BL_FAIL("bl_attention_decode: %d slices (1..256)", n_splits);
@@ -740,6 +760,7 @@ extern "C" int bl_attention_decode(const void* q, const void* k_cache, const voi
     p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n * H * n_splits * dh : nullptr;
     p.counters = counters;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.tail = BlAttnTail{sinks, sink_dtype, gate, ld_gate};
     const int G = H / KV;
     return dispatch<true>(dh, p, dim3(n_splits, KV * ((G + 15) / 16), n), (cudaStream_t)stream);
 }

@@ -75,6 +75,7 @@ struct Params {
     const int* cu_q; const int* ctx_len; const int* block_table; int max_pages;
     const int* tiles;                  // [n][2] (request, first token of the 128-row tile within the request)
     int H, KV, window; float scale_log2;
+    BlAttnTail tail;                   // a sink per head and a gate per (token, head), or nulls
 };
 
 // Bounded wait. False when the bound ran out or another thread of the block has given up. SLEEP: the waiter is one
@@ -545,7 +546,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // one group holds the whole row: out = o / l
             ok = __all_sync(0xffffffffu, ok);
             if (ok && valid) {
-                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                const float inv = bl_attn_tail(p.tail, m, l, (size_t)(q_begin + tok0 + row), head);
                 __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row) * p.H + head) * DH;
 #pragma unroll
                 for (int j = 0; j < DH; j += 8)
@@ -569,7 +570,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const float mm = fmaxf(m, m_o), m_use = mm == -INFINITY ? 0.f : mm;
                 const float a = bl_ex2(m - m_use), a_o = bl_ex2(m_o - m_use);
                 const float total = l * a + l_o * a_o;
-                const float inv = total > 0.f ? 1.0f / total : 0.f;
+                const float inv = bl_attn_tail(p.tail, mm, total, (size_t)(q_begin + tok0 + row), head);
                 const float wa = a * inv, wo = a_o * inv;
                 float r[DH / 2];
 #pragma unroll
@@ -623,6 +624,15 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
                                        const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
                                        int n_tiles, void* out, int T, int n_pages, int H, int KV, int dh, int page_size,
                                        int window, float scale, void* stream) {
+    return bl_attention_prefill_tc_tail(q, k_cache, v_cache, cu_q, ctx_len, block_table, max_pages, tiles, n_tiles, out, T, n_pages,
+                                        H, KV, dh, page_size, window, scale, nullptr, 0, nullptr, 0, stream);
+}
+
+extern "C" int bl_attention_prefill_tc_tail(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                            const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
+                                            int n_tiles, void* out, int T, int n_pages, int H, int KV, int dh, int page_size,
+                                            int window, float scale, const void* sinks, int sink_dtype, const float* gate,
+                                            int ld_gate, void* stream) {
     if (n_tiles <= 0) return 0;
     if ((dh != 64 && dh != 128) || page_size != PAGE)
         BL_FAIL("bl_attention_prefill_tc: head size %d with pages of %d tokens is not built (64 or 128 with 16 only)", dh, page_size);
@@ -635,6 +645,7 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
     Params p;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.tiles = tiles; p.H = H; p.KV = KV; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    p.tail = BlAttnTail{sinks, sink_dtype, gate, ld_gate};
     if (dh == 64) return launch<Shape<64, 2>>(q, k_cache, v_cache, p, n_tiles, T, n_pages, (cudaStream_t)stream);
     return launch<Shape<128, 1>>(q, k_cache, v_cache, p, n_tiles, T, n_pages, (cudaStream_t)stream);
 }

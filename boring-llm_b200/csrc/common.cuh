@@ -56,6 +56,24 @@ __device__ __forceinline__ float bl_silu(float x) { return x / (1.0f + expf(-x))
 // is rounded to bfloat16 (2^-9) anyway and that evaluate it millions of times per step.
 __device__ __forceinline__ float bl_silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
+// What may follow the softmax of an attention row: a sink per head (a learned score whose exponential joins the
+// denominator once, unscaled, with no value) and a gate per (token, head) whose sigmoid multiplies the row's output.
+// bl_attn_tail returns the factor for the row's unnormalised output, given the row's maximum m in the base-2 domain
+// (score * scale * log2 e) and the sum l of 2^(score - m). Null pointers: a plain 1 / l.
+struct BlAttnTail { const void* sinks; int sink_dtype; const float* gate; int ld_gate; };
+__device__ __forceinline__ float bl_attn_tail(const BlAttnTail& t, float m_log2, float l, size_t tok, int head) {
+    float f = 1.f;
+    if (t.sinks) {
+        const float sk = bl_load_any(t.sinks, t.sink_dtype, head) * 1.4426950408889634f;
+        const float mm = fmaxf(m_log2, sk);
+        f = exp2f(m_log2 - mm);                        // a row without keys: 0
+        l = l * f + exp2f(sk - mm);
+    }
+    float inv = l > 0.f ? f / l : 0.f;
+    if (t.gate) inv *= 1.0f / (1.0f + expf(-t.gate[tok * (size_t)t.ld_gate + head]));
+    return inv;
+}
+
 // Programmatic dependent launch. A kernel launched with bl_launch_dependent() may start while its predecessor
 // on the stream is still running; whatever it does before bl_pdl_wait() must touch only data that no earlier
 // kernel of the step writes (weights, the step's index arrays). bl_pdl_wait() returns once the predecessor has

@@ -308,12 +308,24 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
           M, N, K, epilogue, _stream())
 
 
+def _tail(T: int, H: int, sinks: Optional[torch.Tensor], gate: Optional[torch.Tensor]):
+    """The arguments (sinks, their dtype, gate, its row stride) of the attention kernels' `_tail` entry points."""
+    if sinks is not None:
+        _need(sinks, "sinks", None, (H,))
+    ld = 0
+    if gate is not None:
+        if not gate.is_cuda or gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < H:
+            raise KernelError("gate: must be 32-bit CUDA rows [T, >= H] with contiguous rows")
+        ld = gate.stride(0)
+    return _p(sinks), _dt(sinks) if sinks is not None else 0, _p(gate), ld
+
+
 def attention_mma_supported(dtype: torch.dtype, dh: int, page_size: int) -> bool:
     return dtype == torch.bfloat16 and bool(library.load().bl_attention_mma_supported(dh, page_size))
 
 
 def attention_prefill(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles, out, H: int, window: int,
-                      scale: float) -> None:
+                      scale: float, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention for requests with several new tokens. tiles: int32 [n, 2] = (request, first token
     of a 64-token tile among the request's new tokens)."""
     T = q.shape[0]
@@ -322,9 +334,9 @@ def attention_prefill(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles, ou
     _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape); _need(out, "out", torch.bfloat16, (T, H * dh))
     _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
     _need(tiles, "tiles", torch.int32)
-    _call(_lib().bl_attention_prefill, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+    _call(_lib().bl_attention_prefill_tail, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(tiles), tiles.shape[0], _p(out), H, KV, dh, page_size, window,
-          ctypes.c_float(scale), _stream())
+          ctypes.c_float(scale), *_tail(T, H, sinks, gate), _stream())
 
 
 def attention_prefill_tc_supported(dtype: torch.dtype, dh: int, page_size: int) -> bool:
@@ -332,7 +344,7 @@ def attention_prefill_tc_supported(dtype: torch.dtype, dh: int, page_size: int) 
 
 
 def attention_prefill_tc(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles, out, H: int, window: int,
-                         scale: float) -> None:
+                         scale: float, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """The tcgen05 form of `attention_prefill` (head size 64, pages of 16). tiles: int32 [n, 2] = (request,
     first token of a tile of 128 among the request's new tokens); the last entries are launched first."""
     T = q.shape[0]
@@ -341,16 +353,17 @@ def attention_prefill_tc(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles,
     _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape); _need(out, "out", torch.bfloat16, (T, H * dh))
     _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
     _need(tiles, "tiles", torch.int32, (tiles.shape[0], 2))
-    _call(_lib().bl_attention_prefill_tc, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+    _call(_lib().bl_attention_prefill_tc_tail, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(tiles), tiles.shape[0], _p(out), T, n_pages, H, KV, dh, page_size, window,
-          ctypes.c_float(scale), _stream())
+          ctypes.c_float(scale), *_tail(T, H, sinks, gate), _stream())
 
 
 DECODE_CLUSTER_SPLITS = 16     # up to this many slices merge through distributed shared memory (one cluster a request and head group)
 
 
 def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_splits: int, out, H: int, window: int,
-                     scale: float, scratch: Optional[torch.Tensor] = None) -> None:
+                     scale: float, scratch: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
+                     gate: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention for requests with one new token; `reqs` int32 [n] lists them. The keys of each are
     cut into `n_splits` slices. Up to `DECODE_CLUSTER_SPLITS` slices without `scratch`: the slices of a request are
     the blocks of a cluster and merge in shared memory. More slices, or a `scratch` tensor (float32,
@@ -380,9 +393,9 @@ def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_sp
                 raise KernelError("attention_decode: its counters must exist before a capture (run the step once first)")
             # zero once; every launch leaves them at zero again
             counters = _decode_counters[q.device] = torch.zeros(max(n_counters, 4096), dtype=torch.int32, device=q.device)
-    _call(_lib().bl_attention_decode, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+    _call(_lib().bl_attention_decode_tail, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(reqs), n, n_splits, _p(scratch if need else None), _p(counters), _p(out), H, KV, dh,
-          page_size, window, ctypes.c_float(scale), _stream())
+          page_size, window, ctypes.c_float(scale), *_tail(T, H, sinks, gate), _stream())
 
 
 def attention_decode_tma_supported(dtype: torch.dtype, dh: int, page_size: int) -> bool:
@@ -390,7 +403,7 @@ def attention_decode_tma_supported(dtype: torch.dtype, dh: int, page_size: int) 
 
 
 def attention_decode_tma(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_splits: int, out, H: int, window: int,
-                         scale: float) -> None:
+                         scale: float, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """`attention_decode` for head sizes 64 and 128 with keys and values streamed by TMA into per-warp rings and the
     query heads of a key/value head as the columns of the MMAs; 1 to `DECODE_CLUSTER_SPLITS` slices, which are the
     blocks of one cluster and send their partial rows to the blocks that finish them."""
@@ -407,9 +420,9 @@ def attention_decode_tma(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, 
     G = H // KV
     blocks = n * KV * (-(-G // (8 if G <= 8 else 16))) * n_splits
     early = not (n_splits >= DECODE_TMA_LATE_CLUSTER and blocks > _sms())
-    _call(_lib().bl_attention_decode_tma, _p(q), _p(k_cache), _p(v_cache), n_pages, _p(cu_q), _p(ctx_len), _p(block_table),
+    _call(_lib().bl_attention_decode_tma_tail, _p(q), _p(k_cache), _p(v_cache), n_pages, _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(reqs), n, n_splits, _p(out), H, KV, dh, page_size, window, ctypes.c_float(scale),
-          1 if early else 0, _stream())
+          1 if early else 0, *_tail(T, H, sinks, gate), _stream())
 
 
 def attention_decode_tma_resident_blocks(dh: int, heads_per_kv: int) -> int:

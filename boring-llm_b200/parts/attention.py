@@ -66,6 +66,49 @@ def attention_plan(q_lens, ctx_lens, filler=None) -> StepPlan:
         shape=(len(tiles64), len(tiles128), len(singles), longest))
 
 
+def paged_attention(ctx, q, k_cache, v_cache, table, out, H: int, KV: int, dh: int, window: int, scale: float,
+                    sinks=None, gate=None) -> None:
+    """Causal attention of the step's tokens over the paged cache. Tensor-core kernels for bfloat16 where they are built
+    (pages of 16, common head sizes, values of the keys' head size): one launch for the requests with several new tokens
+    (the tcgen05 kernel for head sizes 64 and 128 when the step has many of them), one for those with a single token.
+    Otherwise, and always in float32, the plain kernel. Which requests those are comes from the step's plan
+    (`attention_plan`). `sinks` [H] and `gate` (32-bit logits [T, >= H]) are what may follow the softmax: a score per
+    head that joins the denominator, a sigmoid per (token, head) on the output."""
+    dv = v_cache.shape[3]
+    if not (ctx.fast and dv == dh and ops.attention_mma_supported(q.dtype, dh, k_cache.shape[2])):
+        ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out, H, window, scale, sinks, gate)
+        return
+    plan = ctx.plans.get(PLAN_KEY)
+    if plan is None:                                 # a step put together without asking the parts: plan it now
+        plan = attention_plan(ctx.q_lens, ctx.ctx_lens)
+        plan.arrays = {k: torch.from_numpy(v).to(ctx.device) for k, v in plan.arrays.items()}
+        ctx.plans[PLAN_KEY] = plan
+    tiles64, tiles128, singles = plan.arrays["tiles64"], plan.arrays["tiles128"], plan.arrays["singles"]
+    if tiles64.shape[0]:
+        if tiles128.shape[0] and ops.attention_prefill_tc_supported(q.dtype, dh, k_cache.shape[2]):
+            ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles128, out, H, window, scale, sinks, gate)
+        else:
+            ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles64, out, H, window, scale, sinks, gate)
+    n = singles.shape[0]
+    if n:
+        # as many slices of the keys as fill the device once (the kernel knows how many of its blocks fit)
+        longest = plan.host["longest_single"]
+        if window > 0:
+            longest = min(longest, window + 64)
+        G = H // KV
+        if ops.attention_decode_tma_supported(q.dtype, dh, k_cache.shape[2]):
+            # head sizes 64 and 128: the TMA-fed kernel, which knows how many slices pay for this many requests
+            n_splits = ops.attention_decode_tma_splits(n, KV, G, dh, longest)
+            ops.attention_decode_tma(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out, H, window, scale,
+                                     sinks, gate)
+            return
+        groups = KV * (-(-G // 16))
+        resident = ops.attention_decode_resident_blocks(dh)
+        n_splits = max(1, min(-(-longest // 64), resident // (n * groups), DECODE_MAX_SPLITS))
+        ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out, H, window, scale,
+                             sinks=sinks, gate=gate)
+
+
 class Mixer(Part):
     """Interface of a mixer.
 
@@ -211,46 +254,7 @@ class GQAAttention(Mixer):
         return PLAN_KEY, attention_plan(q_lens, ctx_lens, filler)
 
     def attend(self, ctx, q, k_cache, v_cache, table, out):
-        """Tensor-core kernels for bfloat16 where they are built (pages of 16, common head sizes): one launch for
-        the requests with several new tokens (the tcgen05 kernel for head sizes 64 and 128 when the step has many of them),
-        one for those with a single token. Otherwise, and always in float32, the plain kernel. Which requests those
-        are comes from the step's plan (`attention_plan`)."""
-        if not (ctx.fast and ops.attention_mma_supported(q.dtype, self.dh, k_cache.shape[2])):
-            ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out,
-                                self.H, self.window, self.scale)
-            return
-        plan = ctx.plans.get(PLAN_KEY)
-        if plan is None:                                 # a step put together without asking the parts: plan it now
-            plan = attention_plan(ctx.q_lens, ctx.ctx_lens)
-            plan.arrays = {k: torch.from_numpy(v).to(ctx.device) for k, v in plan.arrays.items()}
-            ctx.plans[PLAN_KEY] = plan
-        tiles64, tiles128, singles = plan.arrays["tiles64"], plan.arrays["tiles128"], plan.arrays["singles"]
-        if tiles64.shape[0]:
-            if tiles128.shape[0] and ops.attention_prefill_tc_supported(q.dtype, self.dh, k_cache.shape[2]):
-                ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles128, out,
-                                         self.H, self.window, self.scale)
-            else:
-                ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles64, out,
-                                      self.H, self.window, self.scale)
-        n = singles.shape[0]
-        if n:
-            # as many slices of the keys as fill the device once (the kernel knows how many of its blocks fit)
-            longest = plan.host["longest_single"]
-            if self.window > 0:
-                longest = min(longest, self.window + 64)
-            G = self.H // self.KV
-            if ops.attention_decode_tma_supported(q.dtype, self.dh, k_cache.shape[2]):
-                # head sizes 64 and 128: the TMA-fed kernel, which knows how many slices pay for this many requests
-                n_splits = ops.attention_decode_tma_splits(n, self.KV, G, self.dh, longest)
-                ops.attention_decode_tma(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out,
-                                         self.H, self.window, self.scale)
-                return
-            groups = self.KV * (-(-G // 16))
-            resident = ops.attention_decode_resident_blocks(self.dh)
-            n_splits = max(1, min(-(-longest // 64), resident // (n * groups), DECODE_MAX_SPLITS))
-            ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out,
-                                 self.H, self.window, self.scale)
-
+        paged_attention(ctx, q, k_cache, v_cache, table, out, self.H, self.KV, self.dh, self.window, self.scale)
 
 class GatedSinkAttention(Mixer):
     """Causal grouped-query attention over the paged cache with the options of newer designs, each a constructor
@@ -342,5 +346,4 @@ class GatedSinkAttention(Mixer):
         self._run(ctx, h, out, cache_layer, write_cache, EPI_NONE)
 
     def attend(self, ctx, q, k_cache, v_cache, table, out, gate):
-        ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out, self.H, self.window,
-                            self.scale, self.sinks, gate)
+        paged_attention(ctx, q, k_cache, v_cache, table, out, self.H, self.KV, self.dk, self.window, self.scale, self.sinks, gate)

@@ -446,3 +446,60 @@ def test_head_norm_and_gates():
         ops.head_norm_gate(o.float().to(DEV), w.float().to(DEV), g.float().to(DEV)[:, 2:2 + H * dv], kind, 1e-5, out, H, dv)
         want = (pf.rms_unit(o.reshape(T, H, dv), 1e-5) * w).reshape(T, H * dv) * fn(g[:, 2:2 + H * dv])
         np.testing.assert_allclose(out.cpu().numpy(), want.numpy(), atol=3e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dh,H,G,window", [(64, 4, 2, 0), (64, 8, 1, 150), (32, 2, 2, 40), (128, 2, 1, 0)])
+def test_sinks_and_gates_in_the_tensor_core_attention_kernels(dh, H, G, window):
+    """Every bfloat16 attention kernel (prefill on mma.sync and on tcgen05, decode on mma.sync with one slice, with a
+    cluster's slices and with slices merged through scratch, decode fed by TMA) with sinks so large that they take about
+    half of every row's weight, and gates: a sink that was left out, or counted once per slice, doubles or halves rows."""
+    from boring_llm_b200.kernels import ops
+    from boring_llm_b200.parts.attention import attention_plan
+    T, page = 300, 16
+    bf = lambda x: x.to(torch.bfloat16).to(torch.float64)
+    q, k, v = bf(rnd(T, H, dh, seed=1)), bf(rnd(T, G, dh, seed=2)), bf(rnd(T, G, dh, seed=3))
+    scale = dh ** -0.5
+    gate = rnd(T, H + 1, seed=5)
+    # a sink near the log of the sum of the row's exponentials: about half the weight
+    sinks = bf(torch.full((H,), math.log(min(T, window or T) / 2) + 0.5, dtype=torch.float64) + rnd(H, seed=4) * 0.3)
+    want = (pf.sink_window_attention(q, k, v, scale, window, sinks) * torch.sigmoid(gate[:, :H])[:, :, None]).reshape(T, H * dh)
+    no_sink = pf.sink_window_attention(q, k, v, scale, window, torch.full((H,), -1e9, dtype=torch.float64))
+    assert (no_sink.reshape(T, -1)[-1].abs().max() > 1.3 * pf.sink_window_attention(q, k, v, scale, window, sinks).reshape(T, -1)[-1].abs().max())
+    n_pages = 24
+    order = list(np.random.default_rng(1).permutation(n_pages))
+    kc, table = paged(k, page, n_pages, order)
+    vc, _ = paged(v, page, n_pages, order)
+    kc, vc = torch.nan_to_num(kc, nan=0.0).to(torch.bfloat16).to(DEV), torch.nan_to_num(vc, nan=0.0).to(torch.bfloat16).to(DEV)
+    qg = q.reshape(T, H * dh).to(torch.bfloat16).to(DEV).contiguous()
+    sg, gg = sinks.float().to(DEV), gate.float().to(DEV)[:, :H]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    tol = dict(atol=2e-2 * float(want.abs().max()), rtol=2e-2)
+    # prefill: one request of T tokens
+    plan = attention_plan([T], [T])
+    tb = i32([table + [-1] * (32 - len(table))])
+    out = torch.zeros(T, H * dh, dtype=torch.bfloat16, device=DEV)
+    ops.attention_prefill(qg, kc, vc, i32([0, T]), i32([T]), tb, i32(plan.arrays["tiles64"]), out, H, window, scale, sg, gg)
+    np.testing.assert_allclose(out.float().cpu().numpy(), want.numpy(), **tol)
+    if ops.attention_prefill_tc_supported(torch.bfloat16, dh, page):
+        out = torch.zeros(T, H * dh, dtype=torch.bfloat16, device=DEV)
+        ops.attention_prefill_tc(qg, kc, vc, i32([0, T]), i32([T]), tb, i32(plan.arrays["tiles128"]), out, H, window, scale, sg, gg)
+        ops.check_status()
+        np.testing.assert_allclose(out.float().cpu().numpy(), want.numpy(), **tol)
+    # decode: three requests on the same pages with contexts of 300, 170 and 33 tokens
+    ctxs = [300, 170, 33]
+    rows = [c - 1 for c in ctxs]
+    qd = qg[rows].contiguous()
+    gd = gate.float().to(DEV)[rows][:, :H]
+    tb3 = tb.repeat(3, 1).contiguous()
+    cu, cl, reqs = i32([0, 1, 2, 3]), i32(ctxs), i32([0, 1, 2])
+    for splits, scratch in ((1, False), (4, False), (5, True)):
+        out = torch.zeros(3, H * dh, dtype=torch.bfloat16, device=DEV)
+        sc = torch.empty(ops.attention_decode_scratch(3, H, dh, splits), device=DEV) if scratch else None
+        ops.attention_decode(qd, kc, vc, cu, cl, tb3, reqs, splits, out, H, window, scale, sc, sinks=sg, gate=gd)
+        np.testing.assert_allclose(out.float().cpu().numpy(), want[rows].numpy(), err_msg=f"mma decode, {splits} slices", **tol)
+    if ops.attention_decode_tma_supported(torch.bfloat16, dh, page):
+        for splits in (1, 3):
+            out = torch.zeros(3, H * dh, dtype=torch.bfloat16, device=DEV)
+            ops.attention_decode_tma(qd, kc, vc, cu, cl, tb3, reqs, splits, out, H, window, scale, sg, gd)
+            ops.check_status()
+            np.testing.assert_allclose(out.float().cpu().numpy(), want[rows].numpy(), err_msg=f"TMA decode, {splits} slices", **tol)
