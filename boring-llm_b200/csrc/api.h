@@ -219,18 +219,19 @@ int bl_attention_plain_ext(const void* q, const void* k_cache, const void* v_cac
 // mean of the squared deviations; statistics in 32-bit.
 int bl_layernorm(const float* x, const int* row_idx, const void* w, int w_dtype, const void* b, int b_dtype,
                  void* y, int y_dtype, int rows, int d, float eps, void* stream);
-// x[r, :] += layer norm(sub[r, :] * sigmoid(gate[r * ld_gate + :])) * w + b: a gate on a sublayer's result, the norm
-// behind the sublayer and the residual sum. gate and b may be null.
-int bl_gated_norm_residual(float* x, const float* sub, const float* gate, int ld_gate, const void* w, int w_dtype,
-                           const void* b, int b_dtype, int rows, int d, float eps, void* stream);
+// x[r, :] += layer norm(sub[r, :] * sigmoid(gate[r * ld_gate + :] + gate_bias[:])) * w + b: a gate on a sublayer's
+// result, the norm behind the sublayer and the residual sum. gate, gate_bias and b may be null.
+int bl_gated_norm_residual(float* x, const float* sub, const float* gate, int ld_gate, const void* gate_bias, int gb_dtype,
+                           const void* w, int w_dtype, const void* b, int b_dtype, int rows, int d, float eps, void* stream);
 // out[e] = sum_{j < n} coeffs[j] * streams[j * stride + e], e < count.
 int bl_depth_mix(const float* streams, long long stride, const void* coeffs, int c_dtype, int n, float* out,
                  long long count, void* stream);
-// y[e] = act(x[e]) (y may be x).
+// y[r, c] = act(x[r, c]) for r < rows, c < cols; rows ld_x and ld_y values apart (y may be x).
 #define BL_ACT_SILU 0
 #define BL_ACT_GELU_ERF 1
 #define BL_ACT_GELU_TANH 2
-int bl_activation(const void* x, int x_dtype, void* y, int y_dtype, long long count, int act, void* stream);
+int bl_activation(const void* x, int x_dtype, long long ld_x, void* y, int y_dtype, long long ld_y, int rows, int cols,
+                  int act, void* stream);
 
 // Rows proj[T, ld] hold a token's joined projections: q in columns 0 .. H * dk, k from off_k (KV * dk), v from off_v
 // (KV * dv). RMS norm of the whole q row and of the whole k row (weights q_norm_w [H * dk], k_norm_w [KV * dk]; null:

@@ -34,14 +34,14 @@ layernorm_kernel(const float* x, const int* __restrict__ row_idx, const void* __
 // x[r, :] += LN(sub[r, :] * sigmoid(gate[r, :])) * w + b: the gate on a sublayer's result, the norm behind the
 // sublayer and the residual sum in one pass. gate may be null (no gate) and has its own row stride.
 __global__ void __launch_bounds__(32 * ROWS_PER_BLOCK)
-gated_norm_residual_kernel(float* x, const float* sub, const float* gate, int ld_gate, const void* __restrict__ w,
-                           int w_dtype, const void* __restrict__ b, int b_dtype, int rows, int d, float eps) {
+gated_norm_residual_kernel(float* x, const float* sub, const float* gate, int ld_gate, const void* __restrict__ gb, int gb_dtype,
+                           const void* __restrict__ w, int w_dtype, const void* __restrict__ b, int b_dtype, int rows, int d, float eps) {
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
     if (r >= rows) return;
     const float* s_row = sub + (size_t)r * d;
     const float* g_row = gate ? gate + (size_t)r * ld_gate : nullptr;
-    auto gated = [&](int i) { return g_row ? s_row[i] * sigmoidf_(g_row[i]) : s_row[i]; };
+    auto gated = [&](int i) { return g_row ? s_row[i] * sigmoidf_(g_row[i] + (gb ? bl_load_any(gb, gb_dtype, i) : 0.f)) : s_row[i]; };
     float s = 0.f;
     for (int i = lane; i < d; i += 32) s += gated(i);
     const float mean = bl_warp_sum(s) / (float)d;
@@ -63,15 +63,122 @@ __global__ void depth_mix_kernel(const float* streams, size_t stride, const void
     }
 }
 
+
+// ---- one block per row, the row in registers (widths that are a multiple of 4, up to ROW_THREADS * 4 * ROW_VECS) ----------
+constexpr int ROW_THREADS = 128, ROW_VECS = 8;
+
+__device__ __forceinline__ float row_block_sum(float v, float* part) {
+    v = bl_warp_sum(v);
+    __syncthreads();                                   // part may still be read from the sum before
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    return (part[0] + part[1]) + (part[2] + part[3]);
+}
+
+__device__ __forceinline__ float4 load4_any(const void* p, int dtype, int i) {
+    if (dtype == BL_F32) return *reinterpret_cast<const float4*>((const float*)p + i);
+    const uint2 u = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)p + i);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
+// MODE 0: y = LN(x[src]) * w + b (y in TY); MODE 1: x += LN(sub * sigmoid(gate)) * w + b (x 32-bit, in place).
+template <typename TY, int MODE>
+__global__ void __launch_bounds__(ROW_THREADS)
+norm_rows_kernel(const float* in, const int* __restrict__ row_idx, const float* gate, int ld_gate, const void* __restrict__ gb,
+                 int gb_dtype, const void* __restrict__ w, int w_dtype, const void* __restrict__ b, int b_dtype, TY* y, float* x,
+                 int d, float eps) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    __shared__ float part[4];
+    const int r = blockIdx.x, n4 = d >> 2;
+    const float4* src = reinterpret_cast<const float4*>(in + (size_t)(row_idx ? row_idx[r] : r) * d);
+    const float4* g4 = gate ? reinterpret_cast<const float4*>(gate + (size_t)r * ld_gate) : nullptr;
+    float4 v[ROW_VECS];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < ROW_VECS; ++j) {
+        const int i = threadIdx.x + j * ROW_THREADS;
+        if (i < n4) {
+            float4 a = src[i];
+            if (MODE == 1 && g4) {
+                float4 g = g4[i];
+                if (gb) { const float4 t = load4_any(gb, gb_dtype, 4 * i); g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w; }
+                a.x *= sigmoidf_(g.x); a.y *= sigmoidf_(g.y); a.z *= sigmoidf_(g.z); a.w *= sigmoidf_(g.w);
+            }
+            v[j] = a;
+            s += (a.x + a.y) + (a.z + a.w);
+        }
+    }
+    const float mean = row_block_sum(s, part) / (float)d;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < ROW_VECS; ++j) {
+        const int i = threadIdx.x + j * ROW_THREADS;
+        if (i < n4) {
+            const float c0 = v[j].x - mean, c1 = v[j].y - mean, c2 = v[j].z - mean, c3 = v[j].w - mean;
+            ss += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+        }
+    }
+    const float inv = 1.0f / sqrtf(row_block_sum(ss, part) / (float)d + eps);
+#pragma unroll
+    for (int j = 0; j < ROW_VECS; ++j) {
+        const int i = threadIdx.x + j * ROW_THREADS;
+        if (i < n4) {
+            const float4 ww = load4_any(w, w_dtype, 4 * i);
+            const float4 bb = b ? load4_any(b, b_dtype, 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float o0 = (v[j].x - mean) * inv * ww.x + bb.x, o1 = (v[j].y - mean) * inv * ww.y + bb.y;
+            const float o2 = (v[j].z - mean) * inv * ww.z + bb.z, o3 = (v[j].w - mean) * inv * ww.w + bb.w;
+            if (MODE == 1) {
+                float4* dst = reinterpret_cast<float4*>(x + (size_t)r * d) + i;
+                float4 cur = *dst;
+                cur.x += o0; cur.y += o1; cur.z += o2; cur.w += o3;
+                *dst = cur;
+            } else if (sizeof(TY) == 4) {
+                reinterpret_cast<float4*>(y + (size_t)r * d)[i] = make_float4(o0, o1, o2, o3);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+                uint2 pk;
+                pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+                reinterpret_cast<uint2*>(y + (size_t)r * d)[i] = pk;
+            }
+        }
+    }
+}
+
+bool rows_fast(int d, const void* a, const void* b2, const void* c, const void* w, const void* bias, int ld_gate) {
+    return d % 4 == 0 && d <= ROW_THREADS * 4 * ROW_VECS && ld_gate % 4 == 0 &&
+           (((uintptr_t)a | (uintptr_t)b2 | (uintptr_t)c | (uintptr_t)w | (uintptr_t)bias) & 15) == 0;
+}
+
+// out[e] = sum_j c[j] * streams[j * stride + e], four values at a time.
+__global__ void depth_mix4_kernel(const float4* streams, size_t stride4, const void* __restrict__ c, int c_dtype, int n,
+                                  float4* out, size_t count4) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count4; e += (size_t)gridDim.x * blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < n; ++j) {
+            const float cj = bl_load_any(c, c_dtype, j);
+            const float4 a = streams[(size_t)j * stride4 + e];
+            acc.x = fmaf(cj, a.x, acc.x); acc.y = fmaf(cj, a.y, acc.y); acc.z = fmaf(cj, a.z, acc.z); acc.w = fmaf(cj, a.w, acc.w);
+        }
+        out[e] = acc;
+    }
+}
+
 template <typename TI, typename TO, int ACT>
-__global__ void activation_kernel(const TI* x, TO* y, size_t count) {
+__global__ void activation_kernel(const TI* x, TO* y, size_t count, int cols, size_t ld_x, size_t ld_y) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x) {
-        const float v = bl_load(x + e);
+        const size_t r = e / cols, c = e % cols;
+        const float v = bl_load(x + r * ld_x + c);
         float o;
         if (ACT == BL_ACT_GELU_ERF) o = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
         else if (ACT == BL_ACT_GELU_TANH) o = 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
         else o = bl_silu(v);
-        bl_store(y + e, o);
+        bl_store(y + r * ld_y + c, o);
     }
 }
 
@@ -87,6 +194,16 @@ extern "C" int bl_layernorm(const float* x, const int* row_idx, const void* w, i
     if (rows <= 0) return 0;
     if (d <= 0) BL_FAIL("bl_layernorm: bad width %d", d);
     cudaStream_t s = (cudaStream_t)stream;
+    if (y_dtype != BL_F32 && y_dtype != BL_BF16) BL_FAIL("bl_layernorm: unknown output dtype %d", y_dtype);
+    if (rows_fast(d, x, y, nullptr, w, b, 0)) {
+        if (y_dtype == BL_F32)
+            BL_CUDA(bl_launch_dependent(norm_rows_kernel<float, 0>, dim3(rows), dim3(ROW_THREADS), 0, s, x, row_idx, nullptr, 0, nullptr, 0, w, w_dtype, b, b_dtype, (float*)y, (float*)nullptr, d, eps));
+        else
+            BL_CUDA(bl_launch_dependent(norm_rows_kernel<__nv_bfloat16, 0>, dim3(rows), dim3(ROW_THREADS), 0, s, x, row_idx, nullptr, 0, nullptr, 0, w, w_dtype, b, b_dtype,
+                                                                             (__nv_bfloat16*)y, (float*)nullptr, d, eps));
+        BL_CHECK_LAUNCH("bl_layernorm");
+        return 0;
+    }
     const int blocks = (rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
     if (y_dtype == BL_F32)
         layernorm_kernel<float><<<blocks, 32 * ROWS_PER_BLOCK, 0, s>>>(x, row_idx, w, w_dtype, b, b_dtype, (float*)y, rows, d, eps);
@@ -99,13 +216,20 @@ extern "C" int bl_layernorm(const float* x, const int* row_idx, const void* w, i
     return 0;
 }
 
-extern "C" int bl_gated_norm_residual(float* x, const float* sub, const float* gate, int ld_gate, const void* w, int w_dtype,
-                                      const void* b, int b_dtype, int rows, int d, float eps, void* stream) {
+extern "C" int bl_gated_norm_residual(float* x, const float* sub, const float* gate, int ld_gate, const void* gate_bias,
+                                      int gb_dtype, const void* w, int w_dtype, const void* b, int b_dtype, int rows, int d,
+                                      float eps, void* stream) {
     if (rows <= 0) return 0;
     if (d <= 0 || (gate && ld_gate < d)) BL_FAIL("bl_gated_norm_residual: bad width %d or gate stride %d", d, ld_gate);
+    if (rows_fast(d, x, sub, gate, w, b, gate ? ld_gate : 0) && ((uintptr_t)gate_bias & 15) == 0) {
+        BL_CUDA(bl_launch_dependent(norm_rows_kernel<float, 1>, dim3(rows), dim3(ROW_THREADS), 0, (cudaStream_t)stream, sub, (const int*)nullptr, gate, ld_gate, gate_bias, gb_dtype, w,
+                                                                                   w_dtype, b, b_dtype, (float*)nullptr, x, d, eps));
+        BL_CHECK_LAUNCH("bl_gated_norm_residual");
+        return 0;
+    }
     const int blocks = (rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
-    gated_norm_residual_kernel<<<blocks, 32 * ROWS_PER_BLOCK, 0, (cudaStream_t)stream>>>(x, sub, gate, ld_gate, w, w_dtype, b,
-                                                                                         b_dtype, rows, d, eps);
+    gated_norm_residual_kernel<<<blocks, 32 * ROWS_PER_BLOCK, 0, (cudaStream_t)stream>>>(x, sub, gate, ld_gate, gate_bias, gb_dtype, w,
+                                                                                         w_dtype, b, b_dtype, rows, d, eps);
     BL_CHECK_LAUNCH("bl_gated_norm_residual");
     return 0;
 }
@@ -114,21 +238,30 @@ extern "C" int bl_depth_mix(const float* streams, long long stride, const void* 
                             long long count, void* stream) {
     if (count <= 0) return 0;
     if (n <= 0 || stride < count) BL_FAIL("bl_depth_mix: %d streams with stride %lld for %lld values", n, stride, count);
+    if (count % 4 == 0 && stride % 4 == 0 && (((uintptr_t)streams | (uintptr_t)out) & 15) == 0) {
+        BL_CUDA(bl_launch_dependent(depth_mix4_kernel, dim3(grid_for((size_t)count / 4, 256)), dim3(256), 0, (cudaStream_t)stream,
+                                    (const float4*)streams, (size_t)stride / 4, coeffs, c_dtype, n, (float4*)out, (size_t)count / 4));
+        BL_CHECK_LAUNCH("bl_depth_mix");
+        return 0;
+    }
     depth_mix_kernel<<<grid_for((size_t)count, 256), 256, 0, (cudaStream_t)stream>>>(streams, (size_t)stride, coeffs, c_dtype, n,
                                                                                      out, (size_t)count);
     BL_CHECK_LAUNCH("bl_depth_mix");
     return 0;
 }
 
-extern "C" int bl_activation(const void* x, int x_dtype, void* y, int y_dtype, long long count, int act, void* stream) {
+extern "C" int bl_activation(const void* x, int x_dtype, long long ld_x, void* y, int y_dtype, long long ld_y, int rows, int cols,
+                             int act, void* stream) {
+    const long long count = (long long)rows * cols;
     if (count <= 0) return 0;
+    if (ld_x < cols || ld_y < cols) BL_FAIL("bl_activation: rows of %d values are %lld and %lld apart", cols, ld_x, ld_y);
     cudaStream_t s = (cudaStream_t)stream;
     const int g = grid_for((size_t)count, 256);
     if (act != BL_ACT_SILU && act != BL_ACT_GELU_ERF && act != BL_ACT_GELU_TANH) BL_FAIL("bl_activation: unknown activation %d", act);
 #define BL_GO3(TI, TO) do { \
-        if (act == BL_ACT_GELU_ERF) activation_kernel<TI, TO, BL_ACT_GELU_ERF><<<g, 256, 0, s>>>((const TI*)x, (TO*)y, (size_t)count); \
-        else if (act == BL_ACT_GELU_TANH) activation_kernel<TI, TO, BL_ACT_GELU_TANH><<<g, 256, 0, s>>>((const TI*)x, (TO*)y, (size_t)count); \
-        else activation_kernel<TI, TO, BL_ACT_SILU><<<g, 256, 0, s>>>((const TI*)x, (TO*)y, (size_t)count); } while (0)
+        if (act == BL_ACT_GELU_ERF) BL_CUDA(bl_launch_dependent(activation_kernel<TI, TO, BL_ACT_GELU_ERF>, dim3(g), dim3(256), 0, s, (const TI*)x, (TO*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y)); \
+        else if (act == BL_ACT_GELU_TANH) BL_CUDA(bl_launch_dependent(activation_kernel<TI, TO, BL_ACT_GELU_TANH>, dim3(g), dim3(256), 0, s, (const TI*)x, (TO*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y)); \
+        else BL_CUDA(bl_launch_dependent(activation_kernel<TI, TO, BL_ACT_SILU>, dim3(g), dim3(256), 0, s, (const TI*)x, (TO*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y)); } while (0)
     if (x_dtype == BL_F32 && y_dtype == BL_F32) BL_GO3(float, float);
     else if (x_dtype == BL_F32 && y_dtype == BL_BF16) BL_GO3(float, __nv_bfloat16);
     else if (x_dtype == BL_BF16 && y_dtype == BL_BF16) BL_GO3(__nv_bfloat16, __nv_bfloat16);

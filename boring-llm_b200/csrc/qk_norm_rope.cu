@@ -25,6 +25,8 @@ qk_norm_rope_write_kernel(const float* proj, int ld, int off_k, int off_v, const
                           const int* __restrict__ tok_req, const int* __restrict__ block_table, int max_pages,
                           const float* __restrict__ inv_freq, int rot_half, int pair_layout, TT* __restrict__ q_out,
                           TT* __restrict__ k_cache, TT* __restrict__ v_cache, int H, int KV, int dk, int dv, int page_size) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
     extern __shared__ float cs[];                      // cos [rot_half], sin [rot_half]
     __shared__ float part[4];
     const int t = blockIdx.x;
@@ -101,9 +103,9 @@ extern "C" int bl_qk_norm_rope_write(const float* proj, int ld, int off_k, int o
         BL_FAIL("bl_qk_norm_rope_write: columns q, k (%d), v (%d) do not fit rows of %d", off_k, off_v, ld);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)(2 * rot_half + 1) * sizeof(float);
-#define BL_GO(TT) qk_norm_rope_write_kernel<TT><<<T, THREADS, smem, s>>>(proj, ld, off_k, off_v, q_norm_w, qw_dtype, k_norm_w, \
-        kw_dtype, eps, positions, tok_req, block_table, max_pages, inv_freq, rot_half, pair_layout, (TT*)q_out, (TT*)k_cache, \
-        (TT*)v_cache, H, KV, dk, dv, page_size)
+#define BL_GO(TT) BL_CUDA(bl_launch_dependent(qk_norm_rope_write_kernel<TT>, dim3(T), dim3(THREADS), smem, s, proj, ld, off_k, off_v, \
+        q_norm_w, qw_dtype, k_norm_w, kw_dtype, eps, positions, tok_req, block_table, max_pages, inv_freq, rot_half, pair_layout, \
+        (TT*)q_out, (TT*)k_cache, (TT*)v_cache, H, KV, dk, dv, page_size))
     if (dtype == BL_F32) BL_GO(float);
     else if (dtype == BL_BF16) BL_GO(__nv_bfloat16);
     else BL_FAIL("bl_qk_norm_rope_write: unknown dtype %d", dtype);

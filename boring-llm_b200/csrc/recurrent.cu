@@ -23,13 +23,27 @@ constexpr int SCAN_SMEM_BYTES = 40 * 1024;
 __device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" :: "r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async16(float* smem, const float* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N)); }
+
+// The tokens of a request pass through shared memory in chunks of `chunk` tokens, two buffers taking turns: while the
+// warps walk one chunk, the next one's q, k, z, v and beta are on their way (cp.async); when it has arrived the block
+// turns z into decays (and scales q, squashes beta) in place, once for all its columns.
 template <bool DELTA>
 __global__ void __launch_bounds__(WARPS * 32)
 recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z, int ldz,
                       const float* beta, int ldb, const float* __restrict__ coef, float z_sign, float q_scale,
                       float* state, size_t slot_stride, const int* __restrict__ slots, const int* __restrict__ cu_q,
-                      float* out, int H, int G, int dk, int dv, int KS, int chunk) {
-    extern __shared__ float sm[];
+                      float* out, int H, int G, int dk, int dv, int KS, int chunk, int vec) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    extern __shared__ __align__(16) float sm[];
     const int r = blockIdx.z, h = blockIdx.y;
     const int t0 = cu_q[r], n = cu_q[r + 1] - t0;
     if (n <= 0) return;
@@ -39,12 +53,39 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
     const int s = lane / CW, cc = lane % CW;
     const int c = (blockIdx.x * WARPS + warp) * CW + cc;
     const bool col_ok = c < dv;
-    float* sq = sm;                          // [chunk, dk] q * q_scale
-    float* sk = sq + (size_t)chunk * dk;     // [chunk, dk]
-    float* sd = sk + (size_t)chunk * dk;     // [chunk, dk] decay
-    float* sv = sd + (size_t)chunk * dk;     // [chunk, cols_blk]
-    float* sb = sv + (size_t)chunk * cols_blk;   // [chunk] beta
+    const int per_tok = 3 * dk + cols_blk + 4;              // q | k | z -> decay | v | beta (+ padding to 16 bytes)
+    const int buf_floats = chunk * per_tok;
     float* S = state + (size_t)slots[r] * slot_stride + (size_t)h * dk * dv;
+    const int col0 = blockIdx.x * cols_blk;
+
+    auto issue = [&](int base, float* buf) {
+        const int m = min(chunk, n - base);
+        for (int tt = warp; tt < m; tt += WARPS) {
+            const size_t tok = (size_t)(t0 + base + tt);
+            float* dst = buf + (size_t)tt * per_tok;
+            const float* gq = q + tok * ldq + gh * dk;
+            const float* gk = k + tok * ldk + gh * dk;
+            const float* gz = z + tok * ldz + h * dk;
+            if (vec) {
+                for (int d = lane * 4; d < dk; d += 128) {
+                    cp_async16(dst + d, gq + d); cp_async16(dst + dk + d, gk + d); cp_async16(dst + 2 * dk + d, gz + d);
+                }
+            } else {
+                for (int d = lane; d < dk; d += 32) {
+                    cp_async4(dst + d, gq + d); cp_async4(dst + dk + d, gk + d); cp_async4(dst + 2 * dk + d, gz + d);
+                }
+            }
+            const float* gv = v + tok * ldv + h * dv + col0;
+            for (int j = lane; j < cols_blk; j += 32) {
+                if (col0 + j < dv) cp_async4(dst + 3 * dk + j, gv + j);
+                else dst[3 * dk + j] = 0.f;
+            }
+            if (DELTA && lane == 0) cp_async4(dst + 3 * dk + cols_blk, beta + tok * ldb + h);
+        }
+        cp_async_commit();
+    };
+
+    issue(0, sm);
     float st[RKMAX];
 #pragma unroll
     for (int i = 0; i < RKMAX; ++i) {
@@ -52,68 +93,85 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
         st[i] = (row < dk && col_ok) ? S[(size_t)row * dv + c] : 0.f;
     }
     const float cf = coef[h];
-    for (int base = 0; base < n; base += chunk) {
+    int which = 0;
+    for (int base = 0; base < n; base += chunk, which ^= 1) {
         const int m = min(chunk, n - base);
+        float* buf = sm + (size_t)which * buf_floats;
+        if (base + chunk < n) { issue(base + chunk, sm + (size_t)(which ^ 1) * buf_floats); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
         for (int idx = threadIdx.x; idx < m * dk; idx += WARPS * 32) {
-            const int tt = idx / dk, d = idx % dk;
-            const size_t tok = (size_t)(t0 + base + tt);
-            sq[idx] = q[tok * ldq + gh * dk + d] * q_scale;
-            sk[idx] = k[tok * ldk + gh * dk + d];
-            sd[idx] = expf(-cf * softplusf_(z_sign * z[tok * ldz + h * dk + d]));
-        }
-        for (int idx = threadIdx.x; idx < m * cols_blk; idx += WARPS * 32) {
-            const int tt = idx / cols_blk, j = idx % cols_blk;
-            const int col = blockIdx.x * cols_blk + j;
-            sv[idx] = col < dv ? v[(size_t)(t0 + base + tt) * ldv + h * dv + col] : 0.f;
+            float* row = buf + (size_t)(idx / dk) * per_tok;
+            const int d = idx % dk;
+            row[d] *= q_scale;
+            row[2 * dk + d] = expf(-cf * softplusf_(z_sign * row[2 * dk + d]));
         }
         if (DELTA)
-            for (int tt = threadIdx.x; tt < m; tt += WARPS * 32) sb[tt] = sigmoidf_(beta[(size_t)(t0 + base + tt) * ldb + h]);
+            for (int tt = threadIdx.x; tt < m; tt += WARPS * 32) {
+                float* b = buf + (size_t)tt * per_tok + 3 * dk + cols_blk;
+                *b = sigmoidf_(*b);
+            }
         __syncthreads();
+        // A token's q, k and decays are fetched into registers while the token before is worked on: the fetches do not
+        // depend on the state, the arithmetic does, and a warp has no other warp to hide its latencies behind.
+        float cq[RKMAX], ck[RKMAX], cd[RKMAX], nq[RKMAX], nk[RKMAX], nd[RKMAX];
+        float cv, cb = 0.f, nv = 0.f, nb = 0.f;
+        auto fetch = [&](int tt, float (&fq)[RKMAX], float (&fk)[RKMAX], float (&fd)[RKMAX], float& fv, float& fb) {
+            const float* pq = buf + (size_t)tt * per_tok;
+#pragma unroll
+            for (int i = 0; i < RKMAX; ++i) {
+                const int row = i * KS + s;
+                const int rr = min(row, dk - 1);
+                const bool ok = row < dk;
+                fq[i] = ok ? pq[rr] : 0.f;
+                fk[i] = ok ? pq[dk + rr] : 0.f;
+                fd[i] = pq[2 * dk + rr];
+            }
+            fv = pq[3 * dk + warp * CW + cc];
+            if (DELTA) fb = pq[3 * dk + cols_blk];
+        };
+        fetch(0, cq, ck, cd, cv, cb);
         for (int tt = 0; tt < m; ++tt) {
-            const float* pq = sq + (size_t)tt * dk;
-            const float* pk = sk + (size_t)tt * dk;
-            const float* pd = sd + (size_t)tt * dk;
-            const float vv = sv[tt * cols_blk + warp * CW + cc];
+            if (tt + 1 < m) fetch(tt + 1, nq, nk, nd, nv, nb);
             float o;
             if (!DELTA) {
-                o = 0.f;
+                float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-                for (int i = 0; i < RKMAX; ++i) {
-                    const int row = i * KS + s;
-                    if (row < dk) {
-                        st[i] = fmaf(pd[row], st[i], pk[row] * vv);
-                        o = fmaf(st[i], pq[row], o);
-                    }
+                for (int i = 0; i < RKMAX; i += 2) {
+                    st[i] = fmaf(cd[i], st[i], ck[i] * cv);
+                    st[i + 1] = fmaf(cd[i + 1], st[i + 1], ck[i + 1] * cv);
+                    o0 = fmaf(st[i], cq[i], o0);
+                    o1 = fmaf(st[i + 1], cq[i + 1], o1);
                 }
+                o = o0 + o1;
                 for (int x = 16; x >= CW; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
             } else {
-                float sk_ = 0.f, sq_ = 0.f, kq = 0.f;
+                float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f, kq0 = 0.f, kq1 = 0.f;
 #pragma unroll
-                for (int i = 0; i < RKMAX; ++i) {
-                    const int row = i * KS + s;
-                    if (row < dk) {
-                        st[i] *= pd[row];
-                        sk_ = fmaf(st[i], pk[row], sk_);
-                        sq_ = fmaf(st[i], pq[row], sq_);
-                        kq = fmaf(pk[row], pq[row], kq);
-                    }
+                for (int i = 0; i < RKMAX; i += 2) {
+                    st[i] *= cd[i];
+                    st[i + 1] *= cd[i + 1];
+                    sk0 = fmaf(st[i], ck[i], sk0); sk1 = fmaf(st[i + 1], ck[i + 1], sk1);
+                    sq0 = fmaf(st[i], cq[i], sq0); sq1 = fmaf(st[i + 1], cq[i + 1], sq1);
+                    kq0 = fmaf(ck[i], cq[i], kq0); kq1 = fmaf(ck[i + 1], cq[i + 1], kq1);
                 }
+                float sk_ = sk0 + sk1, sq_ = sq0 + sq1, kq = kq0 + kq1;
                 for (int x = 16; x >= CW; x >>= 1) {
                     sk_ += __shfl_xor_sync(0xffffffffu, sk_, x);
                     sq_ += __shfl_xor_sync(0xffffffffu, sq_, x);
                     kq += __shfl_xor_sync(0xffffffffu, kq, x);
                 }
-                const float u = sb[tt] * (vv - sk_);
+                const float u = cb * (cv - sk_);
 #pragma unroll
-                for (int i = 0; i < RKMAX; ++i) {
-                    const int row = i * KS + s;
-                    if (row < dk) st[i] = fmaf(pk[row], u, st[i]);
-                }
+                for (int i = 0; i < RKMAX; ++i) st[i] = fmaf(ck[i], u, st[i]);
                 o = fmaf(kq, u, sq_);                  // S^T q after the write: (a S)^T q + (k . q) u
             }
             if (s == 0 && col_ok) out[(size_t)(t0 + base + tt) * H * dv + h * dv + c] = o;
+#pragma unroll
+            for (int i = 0; i < RKMAX; ++i) { cq[i] = nq[i]; ck[i] = nk[i]; cd[i] = nd[i]; }
+            cv = nv; cb = nb;
         }
-        __syncthreads();
+        __syncthreads();                               // the buffer is free for the chunk after next
     }
 #pragma unroll
     for (int i = 0; i < RKMAX; ++i) {
@@ -127,6 +185,8 @@ template <typename TY>
 __global__ void __launch_bounds__(WARPS * 32)
 head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, const float* gate, int ld_gate, int gate_kind,
                       TY* __restrict__ y, int items, int H, int dv, float eps) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
     const int lane = threadIdx.x & 31;
     const int item = blockIdx.x * WARPS + (threadIdx.x >> 5);
     if (item >= items) return;
@@ -151,6 +211,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 conv_silu_unit_kernel(const float* x, int ld, const float* __restrict__ taps, int n_taps, const float* tail, size_t slot_stride,
                       const int* __restrict__ slots, const int* __restrict__ tok_req, const int* __restrict__ cu_q, float* y,
                       int C, int unit_heads, int scaled_heads, int dk, float q_scale, float unit_eps) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
     const int t = blockIdx.x;
     const int r = tok_req[t];
     const int j = t - cu_q[r];
@@ -178,6 +240,8 @@ conv_silu_unit_kernel(const float* x, int ld, const float* __restrict__ taps, in
 // After the step's convolutions have read the tail: the last n_taps - 1 inputs of each request with tokens.
 __global__ void conv_tail_update_kernel(const float* x, int ld, int n_taps, float* tail, size_t slot_stride,
                                         const int* __restrict__ slots, const int* __restrict__ cu_q, int C) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
     const int r = blockIdx.y;
     const int ch = blockIdx.x * blockDim.x + threadIdx.x;
     const int t0 = cu_q[r], n = cu_q[r + 1] - t0;
@@ -210,19 +274,22 @@ extern "C" int bl_recurrent_scan(int rule, const float* q, int ldq, const float*
     int KS = 1;
     while ((dk + KS - 1) / KS > RKMAX) KS *= 2;
     const int CW = 32 / KS, cols_blk = WARPS * CW;
-    const size_t per_token = (size_t)(3 * dk + cols_blk + 1) * sizeof(float);
-    int chunk = (int)(SCAN_SMEM_BYTES / per_token);
+    const size_t per_token = (size_t)(3 * dk + cols_blk + 4) * sizeof(float);
+    int chunk = (int)(SCAN_SMEM_BYTES / (2 * per_token));
     chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
-    const size_t smem = per_token * chunk;
+    const size_t smem = 2 * per_token * chunk;
     if (smem > 48 * 1024) BL_FAIL("bl_recurrent_scan: %d key channels need %zu bytes of shared memory a token", dk, per_token);
+    // 16-byte copies where every row of q, k and z starts on a 16-byte boundary
+    const int vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldz % 4 == 0 &&
+                    (((uintptr_t)q | (uintptr_t)k | (uintptr_t)z) & 15) == 0;
     dim3 grid((dv + cols_blk - 1) / cols_blk, H, R);
     cudaStream_t s = (cudaStream_t)stream;
     if (rule == BL_RULE_GLA)
-        recurrent_scan_kernel<false><<<grid, WARPS * 32, smem, s>>>(q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, coef, z_sign, q_scale,
-            state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk);
+        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<false>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, coef, z_sign, q_scale,
+            state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec));
     else if (rule == BL_RULE_DELTA)
-        recurrent_scan_kernel<true><<<grid, WARPS * 32, smem, s>>>(q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, coef, z_sign, q_scale,
-            state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk);
+        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<true>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, coef, z_sign, q_scale,
+            state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec));
     else
         BL_FAIL("bl_recurrent_scan: unknown rule %d", rule);
     BL_CHECK_LAUNCH("bl_recurrent_scan");
@@ -237,10 +304,10 @@ extern "C" int bl_head_norm_gate(const float* o, const void* w, int w_dtype, con
     const int items = T * H, blocks = (items + WARPS - 1) / WARPS;
     cudaStream_t s = (cudaStream_t)stream;
     if (y_dtype == BL_F32)
-        head_norm_gate_kernel<float><<<blocks, WARPS * 32, 0, s>>>(o, w, w_dtype, gate, ld_gate, gate_kind, (float*)y, items, H, dv, eps);
+        BL_CUDA(bl_launch_dependent(head_norm_gate_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, s, o, w, w_dtype, gate, ld_gate, gate_kind, (float*)y, items, H, dv, eps));
     else if (y_dtype == BL_BF16)
-        head_norm_gate_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, s>>>(o, w, w_dtype, gate, ld_gate, gate_kind,
-                                                                            (__nv_bfloat16*)y, items, H, dv, eps);
+        BL_CUDA(bl_launch_dependent(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, s, o, w, w_dtype, gate,
+                                    ld_gate, gate_kind, (__nv_bfloat16*)y, items, H, dv, eps));
     else
         BL_FAIL("bl_head_norm_gate: unknown output dtype %d", y_dtype);
     BL_CHECK_LAUNCH("bl_head_norm_gate");
@@ -254,8 +321,8 @@ extern "C" int bl_conv_silu_unit(const float* x, int ld, const float* taps, int 
     if (n_taps < 1 || n_taps > MAX_TAPS) BL_FAIL("bl_conv_silu_unit: %d taps, 1..%d are built", n_taps, MAX_TAPS);
     if (C <= 0 || ld < C || unit_heads * dk > C || scaled_heads > unit_heads)
         BL_FAIL("bl_conv_silu_unit: bad sizes C=%d ld=%d heads=%d of %d", C, ld, unit_heads, dk);
-    conv_silu_unit_kernel<<<T, WARPS * 32, 0, (cudaStream_t)stream>>>(x, ld, taps, n_taps, tail, (size_t)slot_stride, slots, tok_req,
-                                                                      cu_q, y, C, unit_heads, scaled_heads, dk, q_scale, unit_eps);
+    BL_CUDA(bl_launch_dependent(conv_silu_unit_kernel, dim3(T), dim3(WARPS * 32), 0, (cudaStream_t)stream, x, ld, taps, n_taps, tail,
+                                (size_t)slot_stride, slots, tok_req, cu_q, y, C, unit_heads, scaled_heads, dk, q_scale, unit_eps));
     BL_CHECK_LAUNCH("bl_conv_silu_unit");
     return 0;
 }
@@ -266,7 +333,8 @@ extern "C" int bl_conv_tail_update(const float* x, int ld, int n_taps, float* ta
     if (n_taps > MAX_TAPS) BL_FAIL("bl_conv_tail_update: %d taps, 1..%d are built", n_taps, MAX_TAPS);
     if (R > 65535) BL_FAIL("bl_conv_tail_update: %d requests are too many for one launch", R);
     dim3 grid((C + 127) / 128, R);
-    conv_tail_update_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, ld, n_taps, tail, (size_t)slot_stride, slots, cu_q, C);
+    BL_CUDA(bl_launch_dependent(conv_tail_update_kernel, grid, dim3(128), 0, (cudaStream_t)stream, x, ld, n_taps, tail,
+                                (size_t)slot_stride, slots, cu_q, C));
     BL_CHECK_LAUNCH("bl_conv_tail_update");
     return 0;
 }

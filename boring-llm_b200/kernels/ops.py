@@ -796,15 +796,18 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor
 
 
 def gated_norm_residual(x: torch.Tensor, sub: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor,
-                        bias: Optional[torch.Tensor], eps: float) -> None:
-    """x += layer norm(sub * sigmoid(gate)) * weight + bias, row by row, in 32-bit (gate None: no gate)."""
+                        bias: Optional[torch.Tensor], eps: float, gate_bias: Optional[torch.Tensor] = None) -> None:
+    """x += layer norm(sub * sigmoid(gate + gate_bias)) * weight + bias, row by row, in 32-bit (gate None: no gate; it
+    may be a range of columns of a wider matrix)."""
     rows, d = x.shape
     _need(x, "x", torch.float32); _need(sub, "sub", torch.float32, (rows, d)); _need(weight, "weight", None, (d,))
     if bias is not None:
         _need(bias, "bias", None, (d,))
     ld = _rows32(gate, "gate", rows, d) if gate is not None else 0
-    _call(_lib().bl_gated_norm_residual, _p(x), _p(sub), _p(gate), ld, _p(weight), _dt(weight), _p(bias),
-          _dt(bias) if bias is not None else 0, rows, d, ctypes.c_float(eps), _stream())
+    if gate_bias is not None:
+        _need(gate_bias, "gate_bias", None, (d,))
+    _call(_lib().bl_gated_norm_residual, _p(x), _p(sub), _p(gate), ld, _p(gate_bias), _dt(gate_bias) if gate_bias is not None else 0,
+          _p(weight), _dt(weight), _p(bias), _dt(bias) if bias is not None else 0, rows, d, ctypes.c_float(eps), _stream())
 
 
 def depth_mix(streams: torch.Tensor, coeffs: torch.Tensor, n: int, out: torch.Tensor) -> None:
@@ -818,9 +821,12 @@ def depth_mix(streams: torch.Tensor, coeffs: torch.Tensor, n: int, out: torch.Te
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, act: int) -> None:
-    """out = silu, the exact (erf) gelu or the tanh gelu of every element of x, evaluated in 32-bit (out may be x)."""
-    _need(x, "x"); _need(out, "out", None, tuple(x.shape))
-    _call(_lib().bl_activation, _p(x), _dt(x), _p(out), _dt(out), ctypes.c_longlong(x.numel()), act, _stream())
+    """out = silu, the exact (erf) gelu or the tanh gelu of every element of x, evaluated in 32-bit (out may be x). x and
+    out are matrices whose rows are contiguous (either may be a range of columns of a wider matrix)."""
+    if x.dim() != 2 or out.shape != x.shape or x.stride(1) != 1 or out.stride(1) != 1 or not (x.is_cuda and out.is_cuda):
+        raise KernelError("activation: x and out must be CUDA matrices of one shape with contiguous rows")
+    _call(_lib().bl_activation, _p(x), _dt(x), ctypes.c_longlong(x.stride(0)), _p(out), _dt(out), ctypes.c_longlong(out.stride(0)),
+          x.shape[0], x.shape[1], act, _stream())
 
 
 def qk_norm_rope_write(proj: torch.Tensor, off_k: int, off_v: int, q_norm_w: Optional[torch.Tensor],
@@ -909,15 +915,15 @@ def conv_tail_update(x: torch.Tensor, n_taps: int, tail: torch.Tensor, slots: to
           cu_q.shape[0] - 1, C, _stream())
 
 
-def linear_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int, fast: bool = True) -> None:
-    """out = act(x @ w.T), the activation evaluated in 32-bit on the product's 32-bit sums."""
-    M = x.shape[0]
-    N = w.shape[0]
-    _need(out, "out", None, (M, N))
-    if out.dtype == torch.float32:
-        gemm(x, w, out, None, EPI_NONE, fast=fast)
-        activation(out, out, act)
-        return
-    sums = torch.empty((M, N), dtype=torch.float32, device=x.device)
+def linear_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int, fast: bool = True):
+    """out = act((x @ w.T)[:, :N]), N = out's columns, the activation evaluated in 32-bit on the product's 32-bit sums.
+    w may have more rows than out has columns: the sums of those further rows are returned as they are (a 32-bit view
+    [M, rows - N]; None when there are none)."""
+    M, N = out.shape
+    rows_w = w.shape[0]
+    if rows_w < N:
+        raise KernelError("linear_act: w has fewer rows than out has columns")
+    sums = torch.empty((M, rows_w), dtype=torch.float32, device=x.device)
     gemm(x, w, sums, None, EPI_NONE, fast=fast)
-    activation(sums, out, act)
+    activation(sums[:, :N], out, act)
+    return sums[:, N:] if rows_w > N else None

@@ -134,6 +134,19 @@ class Mixer(Part):
         or return False to be called with the normed rows as usual."""
         return False
 
+    def join_rows(self, weight) -> None:
+        """For mixers that begin with ONE joined product of their input rows (its matrix in `self.w_in`, its 32-bit sums
+        in `proj`): further rows for that matrix, from a part that reads the same rows (a gate on the mixer's result).
+        After each run their sums are `self.joined_out` (a view [T, rows])."""
+        pad = -self.w_in.shape[0] % 8            # the further columns start on a 16-byte boundary of the 32-bit sums
+        self.n_own = self.w_in.shape[0] + pad
+        self.w_in = torch.cat([self.w_in, self.w_in.new_zeros((pad, self.w_in.shape[1])),
+                               weight.to(device=self.w_in.device, dtype=self.w_in.dtype)], dim=0).contiguous()
+
+    def _joined(self, proj):
+        n_own = getattr(self, "n_own", None)
+        self.joined_out = proj[:, n_own:] if n_own is not None else None
+
     def mix(self, ctx, h, out, cache_layer: Optional[int], write_cache: bool = True) -> None:
         """Writes the result into the 32-bit `out` [T, dim] instead of adding it to a stream (for arrangements that
         treat a sublayer's result before the residual sum). Mixers whose last product can write as well as add
@@ -327,8 +340,9 @@ class GatedSinkAttention(Mixer):
     def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
         T = h.shape[0]
         k_cache, v_cache, table = ctx.kv(cache_layer)
-        proj = ctx.empty((T, self.n_in), torch.float32)
+        proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
         linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        self._joined(proj)
         q = ctx.empty((T, self.H * self.dk))
         ops.qk_norm_rope_write(proj, self.off_k, self.off_v, self.q_norm, self.k_norm, self.qk_norm_eps, ctx.positions,
                                ctx.tok_req, table, self.rotary.inv_freq, self.rotary.rot_half, self.rotary.pair_layout, q,

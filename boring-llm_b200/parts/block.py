@@ -74,6 +74,16 @@ class ResidualGate(Part):
         linear(ctx, h, self.weight, out, self.bias, EPI_BIAS if self.has_bias else EPI_NONE)
         return out
 
+    def join_into(self, part) -> bool:
+        """Hands this gate's matrix to a sublayer whose first product reads the same rows (`part.join_rows`): the gate's
+        logits then come out of that product as further columns (`part.joined_out`), and the bias is added by the kernel
+        that applies the gate. True when the part took it."""
+        if self.weight is None or not hasattr(part, "join_rows"):
+            return False
+        part.join_rows(self.weight)
+        self.weight = None
+        return True
+
 
 class GatedSandwichBlock(Part):
     """Norms on both sides of each sublayer and a gate on its result:
@@ -91,6 +101,7 @@ class GatedSandwichBlock(Part):
         self.ffn_norm, self.ffn, self.ffn_post_norm, self.ffn_gate = ffn_norm, ffn, ffn_post_norm, ffn_gate
         if ffn is not None and (ffn_norm is None or ffn_post_norm is None):
             raise ValueError("GatedSandwichBlock: a feed-forward needs the norms on both of its sides")
+        self._joined = None                      # (mixer's gate joined, feed-forward's gate joined), once the weights are there
 
     def children(self):
         return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.mixer_gate, self.ffn_norm, self.ffn,
@@ -105,16 +116,24 @@ class GatedSandwichBlock(Part):
 
     def forward(self, ctx, x, cache_layer: Optional[int], write_cache: bool = True) -> None:
         ctx.next_norm = None                     # no product of this block may begin a norm for its successor
+        if self._joined is None:                 # the first step: a gate reads what its sublayer reads, so one product serves both
+            self._joined = (self.mixer_gate is not None and self.mixer_gate.join_into(self.mixer),
+                            self.ffn is not None and self.ffn_gate is not None and self.ffn_gate.join_into(self.ffn))
         h = self.mixer_norm.forward(ctx, x)
         sub = ctx.empty(tuple(x.shape), torch.float32)
         self.mixer.mix(ctx, h, sub, cache_layer, write_cache)
-        self._add(ctx, x, sub, h, self.mixer_gate, self.mixer_post_norm)
+        self._add(ctx, x, sub, h, self.mixer_gate, self.mixer_post_norm, self.mixer if self._joined[0] else None)
         if self.ffn is not None:
             h = self.ffn_norm.forward(ctx, x)
             self.ffn.apply(ctx, h, sub)
-            self._add(ctx, x, sub, h, self.ffn_gate, self.ffn_post_norm)
+            self._add(ctx, x, sub, h, self.ffn_gate, self.ffn_post_norm, self.ffn if self._joined[1] else None)
 
     @staticmethod
-    def _add(ctx, x, sub, h, gate, post):
-        g = gate.logits(ctx, h) if gate is not None else None
-        ops.gated_norm_residual(x, sub, g, post.weight, getattr(post, "bias", None), post.eps)
+    def _add(ctx, x, sub, h, gate, post, joined_into):
+        if gate is None:
+            g = gb = None
+        elif joined_into is not None:
+            g, gb = joined_into.joined_out, gate.bias
+        else:
+            g, gb = gate.logits(ctx, h), None
+        ops.gated_norm_residual(x, sub, g, post.weight, getattr(post, "bias", None), post.eps, gb)

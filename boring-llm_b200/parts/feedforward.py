@@ -50,9 +50,18 @@ class DenseMLP(FeedForward):
     def local_specs(self):
         return {"w_up": TensorSpec((self.hidden, self.dim), MATRIX), "w_down": TensorSpec((self.dim, self.hidden), MATRIX)}
 
+    def join_rows(self, weight) -> None:
+        """Further rows for the up product's matrix, from a part that reads the same rows (a gate on this feed-forward's
+        result); after each run their 32-bit sums are `self.joined_out` [T, rows]."""
+        pad = -self.w_up.shape[0] % 8            # the further columns start on a 16-byte boundary of the 32-bit sums
+        self.n_own = self.w_up.shape[0] + pad
+        self.w_up = torch.cat([self.w_up, self.w_up.new_zeros((pad, self.w_up.shape[1])),
+                               weight.to(device=self.w_up.device, dtype=self.w_up.dtype)], dim=0).contiguous()
+
     def _run(self, ctx, h, out, epilogue):
         act = ctx.empty((h.shape[0], self.hidden))
-        ops.linear_act(h, self.w_up, act, self.ACTIVATIONS[self.activation], fast=ctx.fast)
+        rest = ops.linear_act(h, self.w_up, act, self.ACTIVATIONS[self.activation], fast=ctx.fast)
+        self.joined_out = rest[:, self.n_own - self.hidden:] if rest is not None else None
         linear(ctx, act, self.w_down, out, None, epilogue)
 
     def forward(self, ctx, h, residual):

@@ -85,10 +85,11 @@ class GatedLinearAttention(_StateMixer):
     def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
         self._check(write_cache)
         T, H, dk, dv = h.shape[0], self.H, self.dk, self.dv
-        proj = ctx.empty((T, self.off_a + self.rank), torch.float32)
+        proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
         linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        self._joined(proj)
         z = ctx.empty((T, H * dk), torch.float32)
-        ops.gemm_plain(proj[:, self.off_a:], self.a2, z, self.a2_bias, EPI_BIAS)
+        ops.gemm_plain(proj[:, self.off_a:self.off_a + self.rank], self.a2, z, self.a2_bias, EPI_BIAS)
         o = ctx.empty((T, H * dv), torch.float32)
         ops.recurrent_scan(ops.RULE_GLA, proj[:, :self.off_k], proj[:, self.off_k:self.off_v], proj[:, self.off_v:self.off_g],
                            z, None, self.coef, -1.0, dk ** -0.5, ctx.state(cache_layer), ctx.slots, ctx.cu_q, o, H, H, dk, dv)
@@ -153,8 +154,9 @@ class ChannelDeltaRule(_StateMixer):
     def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
         self._check(write_cache)
         T, H, G, dk, dv, C = h.shape[0], self.H, self.G, self.dk, self.dv, self.C
-        proj = ctx.empty((T, self.off_g + self.gate_rank), torch.float32)
+        proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
         linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        self._joined(proj)
         state = ctx.state(cache_layer)
         tail = state[:, H * dk * dv:]
         qkv = ctx.empty((T, C), torch.float32)
@@ -163,7 +165,7 @@ class ChannelDeltaRule(_StateMixer):
         z = ctx.empty((T, H * dk), torch.float32)
         ops.gemm_plain(proj[:, self.off_a:self.off_g], self.a2, z, self.dt_bias, EPI_BIAS)
         glog = ctx.empty((T, H * dv), torch.float32)
-        ops.gemm_plain(proj[:, self.off_g:], self.g2, glog, None, EPI_NONE)
+        ops.gemm_plain(proj[:, self.off_g:self.off_g + self.gate_rank], self.g2, glog, None, EPI_NONE)
         o = ctx.empty((T, H * dv), torch.float32)
         ops.recurrent_scan(ops.RULE_DELTA, qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], z,
                            proj[:, self.off_b:self.off_a], self.coef, 1.0, 1.0, state, ctx.slots, ctx.cu_q, o, H, G, dk, dv)

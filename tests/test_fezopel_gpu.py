@@ -219,6 +219,12 @@ def test_layer_norm_gated_residual_depth_mix_and_activations():
         ops.gated_norm_residual(stream, sub.float().to(DEV), gate.float().to(DEV)[:, 1:d + 1], wg, bg, 1e-5)
         want = x + pf.layer_norm(sub * torch.sigmoid(gate[:, 1:d + 1]), w, b, 1e-5)
         np.testing.assert_allclose(stream.cpu().numpy(), want.numpy(), atol=3e-5, rtol=1e-5)
+        gb = rnd(d, seed=9)                              # the gate's bias added by the kernel, the logits without it
+        stream = xg.clone()
+        ops.gated_norm_residual(stream, sub.float().to(DEV), (gate[:, 1:d + 1] - gb).float().to(DEV).contiguous(), wg, None, 1e-5,
+                                gb.float().to(DEV))
+        want = x + pf.layer_norm(sub * torch.sigmoid(gate[:, 1:d + 1]), w, 0.0, 1e-5)
+        np.testing.assert_allclose(stream.cpu().numpy(), want.numpy(), atol=3e-5, rtol=1e-5)
     streams, c = rnd(5, 7, 12, seed=6), rnd(4, seed=7)
     sg = streams.float().to(DEV)
     ops.depth_mix(sg, c.float().to(DEV), 4, sg[4])
