@@ -245,14 +245,14 @@ int bl_qk_norm_rope_write(const float* proj, int ld, int off_k, int off_v, const
 
 // Linear recurrences over a matrix state per head kept in state slots (recurrent.cu). Request r owns tokens
 // cu_q[r] .. cu_q[r + 1] - 1 and the slot slots[r]; its state S [H, dk, dv] starts at state + slots[r] * slot_stride.
-// q, k: [T, G * dk] (query/key head of head h: h / (H / G)), v: [T, H * dv], z: [T, H * dk] (the decay's
-// pre-activation: a = exp(-coef[h] * softplus(z_sign * z))), beta: [T, H] logits (delta rule only), each with its own
-// row stride; out: [T, H * dv] 32-bit.
+// q, k: [T, G * dk] (query/key head of head h: h / (H / G)), v: [T, H * dv], a: [T, H * dk] (the decays, see
+// bl_gemm_plain_decay), beta: [T, H] logits (delta rule only), each with its own row stride; out: [T, H * dv] 32-bit.
 #define BL_RULE_GLA 0      // S <- diag(a) S + k v^T; o = S^T (q * q_scale)
 #define BL_RULE_DELTA 1    // S <- diag(a) S; u = sigmoid(beta) (v - S^T k); S <- S + k u^T; o = S^T (q * q_scale)
+int bl_gemm_plain_decay(const float* x, int ldx, const void* w, int w_dtype, const void* bias, int bias_dtype,
+                        float* out, int M, int N, int K, const float* coef, int group, float sign, void* stream);
 int bl_recurrent_scan(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
-                      const float* z, int ldz, const float* beta, int ldb, const float* coef, float z_sign,
-                      float q_scale, float* state, long long slot_stride, const int* slots, const int* cu_q, int R,
+                      const float* a, int lda, const float* beta, int ldb, float q_scale, float* state, long long slot_stride, const int* slots, const int* cu_q, int R,
                       float* out, int H, int G, int dk, int dv, void* stream);
 // y[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[:] * gate(g[t * ld_gate + h * dv + :]) (gate null: none).
 #define BL_GATE_SIGMOID 0

@@ -14,7 +14,8 @@ constexpr int TM = 64, TN = 64, TK = 16;
 template <typename TX, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void* __restrict__ bias,
-                  int bias_dtype, TO* __restrict__ out, int M, int N, int K, int ldx) {
+                  int bias_dtype, TO* __restrict__ out, int M, int N, int K, int ldx,
+                  const float* __restrict__ coef, int group, float sign) {
     __shared__ float xs[TK][TM + 1];
     __shared__ float ws[TK][TN + 1];
     __shared__ float us[EPI == BL_EPI_SWIGLU ? TK : 1][TN + 1];
@@ -70,6 +71,11 @@ gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void
             if (EPI == BL_EPI_BIAS) v += bl_load_any(bias, bias_dtype, n);
             if (EPI == BL_EPI_RESIDUAL) v += bl_load(dst);
             if (EPI == BL_EPI_SWIGLU) v = bl_silu(v) * acu[i][j];
+            if (EPI == BL_EPI_DECAY) {                 // exp(-coef[head] * softplus(sign * (acc + bias))), head = n / group
+                if (bias) v += bl_load_any(bias, bias_dtype, n);
+                const float u = sign * v;
+                v = expf(-coef[n / group] * (u > 20.f ? u : log1pf(expf(u))));
+            }
             bl_store(dst, v);
         }
     }
@@ -77,15 +83,16 @@ gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void
 
 template <typename TX, typename TW, typename TO>
 int launch_epi(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
-               int M, int N, int K, int ldx, int epi, cudaStream_t s) {
+               int M, int N, int K, int ldx, int epi, cudaStream_t s, const float* coef = nullptr, int group = 1, float sign = 1.f) {
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
 #define BL_GO(E) gemm_plain_kernel<TX, TW, TO, E><<<grid, 256, 0, s>>>( \
-        (const TX*)x, (const TW*)w, bias, bias_dtype, (TO*)out, M, N, K, ldx)
+        (const TX*)x, (const TW*)w, bias, bias_dtype, (TO*)out, M, N, K, ldx, coef, group, sign)
     switch (epi) {
         case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
         case BL_EPI_BIAS: BL_GO(BL_EPI_BIAS); break;
         case BL_EPI_RESIDUAL: BL_GO(BL_EPI_RESIDUAL); break;
         case BL_EPI_SWIGLU: BL_GO(BL_EPI_SWIGLU); break;
+        case BL_EPI_DECAY: BL_GO(BL_EPI_DECAY); break;
         default: BL_FAIL("bl_gemm_plain: unknown epilogue %d", epi);
     }
 #undef BL_GO
@@ -129,4 +136,17 @@ extern "C" int bl_gemm_plain_ld(const void* x, int x_dtype, int ldx, const void*
     if (x_dtype == BL_F32 && w_dtype == BL_BF16)
         return launch_out<float, __nv_bfloat16>(x, w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, epilogue, s);
     BL_FAIL("bl_gemm_plain: unsupported input dtypes x=%d w=%d", x_dtype, w_dtype);
+}
+
+// out[m, n] = exp(-coef[n / group] * softplus(sign * (x[m, :] . W[n, :] + bias[n]))), 32-bit: the decays of a linear
+// recurrence from their pre-activation, as the epilogue of the product that makes it (x 32-bit rows ldx apart).
+extern "C" int bl_gemm_plain_decay(const float* x, int ldx, const void* w, int w_dtype, const void* bias, int bias_dtype,
+                                   float* out, int M, int N, int K, const float* coef, int group, float sign, void* stream) {
+    if (M <= 0) return 0;
+    if (N <= 0 || K <= 0 || ldx < K || group <= 0 || N % group != 0 || coef == nullptr)
+        BL_FAIL("bl_gemm_plain_decay: bad sizes N=%d K=%d ldx=%d group=%d", N, K, ldx, group);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w_dtype == BL_F32) return launch_epi<float, float, float>(x, w, bias, bias_dtype, out, M, N, K, ldx, BL_EPI_DECAY, s, coef, group, sign);
+    if (w_dtype == BL_BF16) return launch_epi<float, __nv_bfloat16, float>(x, w, bias, bias_dtype, out, M, N, K, ldx, BL_EPI_DECAY, s, coef, group, sign);
+    BL_FAIL("bl_gemm_plain_decay: unknown matrix dtype %d", w_dtype);
 }

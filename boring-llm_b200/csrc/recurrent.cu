@@ -3,8 +3,9 @@
 // the batch; a request without tokens is left alone). Two rules share one kernel:
 //   gated linear attention   S <- diag(a) S + k v^T;                                   o = S^T q
 //   gated delta rule         S <- diag(a) S;  u = beta (v - S^T k);  S <- S + k u^T;   o = S^T q
-// with a decay per key channel a = exp(-coef[head] * softplus(sign * z)) from the decay's pre-activation z (sign -1,
-// coef 1 / tau gives sigmoid(z)^(1 / tau)). State, decays, gates and all sums are 32-bit. The columns of S are
+// with a decay per key channel a, given per token, head and channel (the product that makes its pre-activation z turns it
+// into exp(-coef[head] * softplus(sign * z)); sign -1, coef 1 / tau gives sigmoid(z)^(1 / tau)). State, decays, gates and
+// all sums are 32-bit. The columns of S are
 // independent of one another, so a block owns a few columns of one (request, head) and walks the request's tokens in
 // order; a column's rows are spread over KS lanes of a warp that add up with a fixed butterfly. What a token's result is
 // does not depend on the batch or on how the tokens were cut into steps.
@@ -20,7 +21,6 @@ constexpr int RKMAX = 16;          // rows of a column that one lane holds
 constexpr int MAX_TAPS = 16;
 constexpr int SCAN_SMEM_BYTES = 40 * 1024;
 
-__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
@@ -34,11 +34,11 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 
 // The tokens of a request pass through shared memory in chunks of `chunk` tokens, two buffers taking turns: while the
 // warps walk one chunk, the next one's q, k, z, v and beta are on their way (cp.async); when it has arrived the block
-// turns z into decays (and scales q, squashes beta) in place, once for all its columns.
+// squashes beta in place, once for all its columns.
 template <bool DELTA>
 __global__ void __launch_bounds__(WARPS * 32)
 recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z, int ldz,
-                      const float* beta, int ldb, const float* __restrict__ coef, float z_sign, float q_scale,
+                      const float* beta, int ldb, float q_scale,
                       float* state, size_t slot_stride, const int* __restrict__ slots, const int* __restrict__ cu_q,
                       float* out, int H, int G, int dk, int dv, int KS, int chunk, int vec) {
     bl_pdl_trigger();
@@ -53,7 +53,7 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
     const int s = lane / CW, cc = lane % CW;
     const int c = (blockIdx.x * WARPS + warp) * CW + cc;
     const bool col_ok = c < dv;
-    const int per_tok = 3 * dk + cols_blk + 4;              // q | k | z -> decay | v | beta (+ padding to 16 bytes)
+    const int per_tok = 3 * dk + cols_blk + 4;              // q | k | decay | v | beta (+ padding to 16 bytes)
     const int buf_floats = chunk * per_tok;
     float* S = state + (size_t)slots[r] * slot_stride + (size_t)h * dk * dv;
     const int col0 = blockIdx.x * cols_blk;
@@ -92,7 +92,6 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
         const int row = i * KS + s;
         st[i] = (row < dk && col_ok) ? S[(size_t)row * dv + c] : 0.f;
     }
-    const float cf = coef[h];
     int which = 0;
     for (int base = 0; base < n; base += chunk, which ^= 1) {
         const int m = min(chunk, n - base);
@@ -100,18 +99,13 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
         if (base + chunk < n) { issue(base + chunk, sm + (size_t)(which ^ 1) * buf_floats); cp_async_wait<1>(); }
         else cp_async_wait<0>();
         __syncthreads();
-        for (int idx = threadIdx.x; idx < m * dk; idx += WARPS * 32) {
-            float* row = buf + (size_t)(idx / dk) * per_tok;
-            const int d = idx % dk;
-            row[d] *= q_scale;
-            row[2 * dk + d] = expf(-cf * softplusf_(z_sign * row[2 * dk + d]));
-        }
-        if (DELTA)
+        if (DELTA) {
             for (int tt = threadIdx.x; tt < m; tt += WARPS * 32) {
                 float* b = buf + (size_t)tt * per_tok + 3 * dk + cols_blk;
                 *b = sigmoidf_(*b);
             }
-        __syncthreads();
+            __syncthreads();
+        }
         // A token's q, k and decays are fetched into registers while the token before is worked on: the fetches do not
         // depend on the state, the arithmetic does, and a warp has no other warp to hide its latencies behind.
         float cq[RKMAX], ck[RKMAX], cd[RKMAX], nq[RKMAX], nk[RKMAX], nd[RKMAX];
@@ -166,7 +160,7 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
                 for (int i = 0; i < RKMAX; ++i) st[i] = fmaf(ck[i], u, st[i]);
                 o = fmaf(kq, u, sq_);                  // S^T q after the write: (a S)^T q + (k . q) u
             }
-            if (s == 0 && col_ok) out[(size_t)(t0 + base + tt) * H * dv + h * dv + c] = o;
+            if (s == 0 && col_ok) out[(size_t)(t0 + base + tt) * H * dv + h * dv + c] = o * q_scale;
 #pragma unroll
             for (int i = 0; i < RKMAX; ++i) { cq[i] = nq[i]; ck[i] = nk[i]; cd[i] = nd[i]; }
             cv = nv; cb = nb;
@@ -178,6 +172,149 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
         const int row = i * KS + s;
         if (row < dk && col_ok) S[(size_t)row * dv + c] = st[i];
     }
+}
+
+// The same walk for key sizes that split evenly: a lane holds RK4 * 4 CONSECUTIVE rows of its column (dk = KS * RK4 * 4),
+// so a token's q, k and decays reach its registers as 16-byte loads at fixed offsets, two tokens' registers take turns
+// (no copies), and the dot products run in two chains. A warp has no other warp on its scheduler to hide latencies
+// behind (a request gives H * dv / (WARPS * CW) blocks): what counts is the number of instructions per token.
+template <bool DELTA, int RK4>
+__global__ void __launch_bounds__(WARPS * 32)
+recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z, int ldz,
+                          const float* beta, int ldb, float q_scale,
+                          float* state, size_t slot_stride, const int* __restrict__ slots, const int* __restrict__ cu_q,
+                          float* out, int H, int G, int dk, int dv, int KS, int chunk, int vec) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    constexpr int RK = RK4 * 4;
+    const int r = blockIdx.z, h = blockIdx.y;
+    const int t0 = cu_q[r], n = cu_q[r + 1] - t0;
+    if (n <= 0) return;
+    const int gh = h / (H / G);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int CW = 32 / KS, cols_blk = WARPS * CW;
+    const int s = lane / CW, cc = lane % CW;
+    const int c = (blockIdx.x * WARPS + warp) * CW + cc;
+    const bool col_ok = c < dv;
+    const int per_tok = 3 * dk + cols_blk + 4;
+    const int buf_floats = chunk * per_tok;
+    float* S = state + (size_t)slots[r] * slot_stride + (size_t)h * dk * dv;
+    const int col0 = blockIdx.x * cols_blk;
+    const int row0 = s * RK;
+
+    auto issue = [&](int base, float* buf) {
+        const int m = min(chunk, n - base);
+        for (int tt = warp; tt < m; tt += WARPS) {
+            const size_t tok = (size_t)(t0 + base + tt);
+            float* dst = buf + (size_t)tt * per_tok;
+            const float* gq = q + tok * ldq + gh * dk;
+            const float* gk = k + tok * ldk + gh * dk;
+            const float* gz = z + tok * ldz + h * dk;
+            if (vec) {
+                for (int d = lane * 4; d < dk; d += 128) {
+                    cp_async16(dst + d, gq + d); cp_async16(dst + dk + d, gk + d); cp_async16(dst + 2 * dk + d, gz + d);
+                }
+            } else {
+                for (int d = lane; d < dk; d += 32) {
+                    cp_async4(dst + d, gq + d); cp_async4(dst + dk + d, gk + d); cp_async4(dst + 2 * dk + d, gz + d);
+                }
+            }
+            const float* gv = v + tok * ldv + h * dv + col0;
+            for (int j = lane; j < cols_blk; j += 32) {
+                if (col0 + j < dv) cp_async4(dst + 3 * dk + j, gv + j);
+                else dst[3 * dk + j] = 0.f;
+            }
+            if (DELTA && lane == 0) cp_async4(dst + 3 * dk + cols_blk, beta + tok * ldb + h);
+        }
+        cp_async_commit();
+    };
+
+    issue(0, sm);
+    float st[RK];
+#pragma unroll
+    for (int i = 0; i < RK; ++i) st[i] = col_ok ? S[(size_t)(row0 + i) * dv + c] : 0.f;
+    const int v_off = 3 * dk + warp * CW + cc, b_off = 3 * dk + cols_blk;
+    const int dk4 = dk >> 2;
+
+    struct Tok { float4 q[RK4], k[RK4], d[RK4]; float v, b; };
+    auto fetch = [&](const float* tokp, Tok& t) {
+        const float4* p4 = reinterpret_cast<const float4*>(tokp + row0);
+#pragma unroll
+        for (int j = 0; j < RK4; ++j) { t.q[j] = p4[j]; t.k[j] = p4[dk4 + j]; t.d[j] = p4[2 * dk4 + j]; }
+        t.v = tokp[v_off];
+        t.b = DELTA ? tokp[b_off] : 0.f;
+    };
+    auto step = [&](const Tok& t, size_t tok) {
+        const float* tq = reinterpret_cast<const float*>(t.q);
+        const float* tk = reinterpret_cast<const float*>(t.k);
+        const float* td = reinterpret_cast<const float*>(t.d);
+        float o;
+        if (!DELTA) {
+            float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < RK; i += 2) {
+                st[i] = fmaf(td[i], st[i], tk[i] * t.v);
+                st[i + 1] = fmaf(td[i + 1], st[i + 1], tk[i + 1] * t.v);
+                o0 = fmaf(st[i], tq[i], o0);
+                o1 = fmaf(st[i + 1], tq[i + 1], o1);
+            }
+            o = o0 + o1;
+            for (int x = 16; x >= CW; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+        } else {
+            float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f, kq0 = 0.f, kq1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < RK; i += 2) {
+                st[i] *= td[i];
+                st[i + 1] *= td[i + 1];
+                sk0 = fmaf(st[i], tk[i], sk0); sk1 = fmaf(st[i + 1], tk[i + 1], sk1);
+                sq0 = fmaf(st[i], tq[i], sq0); sq1 = fmaf(st[i + 1], tq[i + 1], sq1);
+                kq0 = fmaf(tk[i], tq[i], kq0); kq1 = fmaf(tk[i + 1], tq[i + 1], kq1);
+            }
+            float sk_ = sk0 + sk1, sq_ = sq0 + sq1, kq = kq0 + kq1;
+            for (int x = 16; x >= CW; x >>= 1) {
+                sk_ += __shfl_xor_sync(0xffffffffu, sk_, x);
+                sq_ += __shfl_xor_sync(0xffffffffu, sq_, x);
+                kq += __shfl_xor_sync(0xffffffffu, kq, x);
+            }
+            const float u = t.b * (t.v - sk_);
+#pragma unroll
+            for (int i = 0; i < RK; ++i) st[i] = fmaf(tk[i], u, st[i]);
+            o = fmaf(kq, u, sq_);
+        }
+        if (s == 0 && col_ok) out[tok * H * dv + h * dv + c] = o * q_scale;
+    };
+
+    int which = 0;
+    for (int base = 0; base < n; base += chunk, which ^= 1) {
+        const int m = min(chunk, n - base);
+        float* buf = sm + (size_t)which * buf_floats;
+        if (base + chunk < n) { issue(base + chunk, sm + (size_t)(which ^ 1) * buf_floats); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+        if (DELTA) {
+            for (int tt = threadIdx.x; tt < m; tt += WARPS * 32) {
+                float* b = buf + (size_t)tt * per_tok + b_off;
+                *b = sigmoidf_(*b);
+            }
+            __syncthreads();
+        }
+        Tok ta, tb;
+        fetch(buf, ta);
+        const size_t tok0 = (size_t)(t0 + base);
+        int tt = 0;
+        for (; tt + 1 < m; tt += 2) {
+            fetch(buf + (size_t)(tt + 1) * per_tok, tb);
+            step(ta, tok0 + tt);
+            if (tt + 2 < m) fetch(buf + (size_t)(tt + 2) * per_tok, ta);
+            step(tb, tok0 + tt + 1);
+        }
+        if (tt < m) step(ta, tok0 + tt);
+        __syncthreads();                               // the buffer is free for the chunk after next
+    }
+#pragma unroll
+    for (int i = 0; i < RK; ++i)
+        if (col_ok) S[(size_t)(row0 + i) * dv + c] = st[i];
 }
 
 // y[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[:] * gate(g[t, h, :]); one warp per (token, head).
@@ -263,8 +400,7 @@ __global__ void conv_tail_update_kernel(const float* x, int ld, int n_taps, floa
 }  // namespace
 
 extern "C" int bl_recurrent_scan(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
-                                 const float* z, int ldz, const float* beta, int ldb, const float* coef, float z_sign,
-                                 float q_scale, float* state, long long slot_stride, const int* slots, const int* cu_q, int R,
+                                 const float* z, int ldz, const float* beta, int ldb, float q_scale, float* state, long long slot_stride, const int* slots, const int* cu_q, int R,
                                  float* out, int H, int G, int dk, int dv, void* stream) {
     if (R <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || dk <= 0 || dv <= 0) BL_FAIL("bl_recurrent_scan: bad sizes H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
@@ -284,11 +420,27 @@ extern "C" int bl_recurrent_scan(int rule, const float* q, int ldq, const float*
                     (((uintptr_t)q | (uintptr_t)k | (uintptr_t)z) & 15) == 0;
     dim3 grid((dv + cols_blk - 1) / cols_blk, H, R);
     cudaStream_t s = (cudaStream_t)stream;
+    if (rule != BL_RULE_GLA && rule != BL_RULE_DELTA) BL_FAIL("bl_recurrent_scan: unknown rule %d", rule);
+    if (dk % (4 * KS) == 0) {                          // a lane's rows are whole groups of four
+        const int rk4 = dk / (4 * KS);
+#define BL_SCAN(D, R4) BL_CUDA(bl_launch_dependent(recurrent_scan_vec_kernel<D, R4>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, \
+        z, ldz, beta, ldb, q_scale, state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec))
+        const bool dl = rule == BL_RULE_DELTA;
+        switch (rk4) {
+            case 1: if (dl) BL_SCAN(true, 1); else BL_SCAN(false, 1); break;
+            case 2: if (dl) BL_SCAN(true, 2); else BL_SCAN(false, 2); break;
+            case 3: if (dl) BL_SCAN(true, 3); else BL_SCAN(false, 3); break;
+            default: if (dl) BL_SCAN(true, 4); else BL_SCAN(false, 4); break;
+        }
+#undef BL_SCAN
+        BL_CHECK_LAUNCH("bl_recurrent_scan");
+        return 0;
+    }
     if (rule == BL_RULE_GLA)
-        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<false>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, coef, z_sign, q_scale,
+        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<false>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale,
             state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec));
     else if (rule == BL_RULE_DELTA)
-        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<true>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, coef, z_sign, q_scale,
+        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<true>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale,
             state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec));
     else
         BL_FAIL("bl_recurrent_scan: unknown rule %d", rule);

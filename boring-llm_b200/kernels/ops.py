@@ -858,23 +858,39 @@ def qk_norm_rope_write(proj: torch.Tensor, off_k: int, off_v: int, q_norm_w: Opt
           _dt(q_out), T, H, KV, dk, dv, page_size, _stream())
 
 
-def recurrent_scan(rule: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, beta: Optional[torch.Tensor],
-                   coef: torch.Tensor, z_sign: float, q_scale: float, state: torch.Tensor, slots: torch.Tensor,
-                   cu_q: torch.Tensor, out: torch.Tensor, H: int, G: int, dk: int, dv: int) -> None:
+def gemm_plain_decay(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], coef: torch.Tensor, group: int, sign: float,
+                     out: torch.Tensor) -> None:
+    """out[m, n] = exp(-coef[n // group] * softplus(sign * (x[m] . w[n] + bias[n]))), 32-bit: the decays of a linear
+    recurrence as the epilogue of the product that makes their pre-activation (sign -1, coef 1 / tau: sigmoid(z)^(1 / tau)).
+    x: 32-bit rows, possibly a column range of a wider matrix."""
+    M, K = x.shape
+    N = out.shape[1]
+    ld = _rows32(x, "x", M, K)
+    _need(w, "w", None, (N, K)); _need(out, "out", torch.float32, (M, N)); _need(coef, "coef", torch.float32, (N // group,))
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    _call(_lib().bl_gemm_plain_decay, _p(x), ld, _p(w), _dt(w), _p(bias), _dt(bias) if bias is not None else 0, _p(out), M, N, K,
+          _p(coef), group, ctypes.c_float(sign), _stream())
+
+
+def recurrent_scan(rule: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: Optional[torch.Tensor],
+                   q_scale: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, out: torch.Tensor,
+                   H: int, G: int, dk: int, dv: int) -> None:
     """A linear recurrence over a matrix state per head and request (`RULE_GLA`, `RULE_DELTA`; see `bl_recurrent_scan`).
-    q, k [T, G * dk], v [T, H * dv], z [T, H * dk], beta [T, H] (logits): 32-bit rows, possibly column ranges of a
-    wider matrix. state: [slots, >= H * dk * dv] 32-bit, the matrix state first in each slot. out [T, H * dv] 32-bit."""
+    q, k [T, G * dk], v [T, H * dv], decay [T, H * dk] (in (0, 1], see `gemm_plain_decay`), beta [T, H] (logits): 32-bit
+    rows, possibly column ranges of a wider matrix. state: [slots, >= H * dk * dv] 32-bit, the matrix state first in each
+    slot. out [T, H * dv] 32-bit, already times q_scale."""
     T = out.shape[0]
     R = cu_q.shape[0] - 1
     ldq, ldk, ldv, ldz = (_rows32(q, "q", T, G * dk), _rows32(k, "k", T, G * dk), _rows32(v, "v", T, H * dv),
-                          _rows32(z, "z", T, H * dk))
+                          _rows32(decay, "decay", T, H * dk))
     ldb = _rows32(beta, "beta", T, H) if beta is not None else 0
-    _need(coef, "coef", torch.float32, (H,)); _need(slots, "slots", torch.int32); _need(cu_q, "cu_q", torch.int32)
+    _need(slots, "slots", torch.int32); _need(cu_q, "cu_q", torch.int32)
     _need(out, "out", torch.float32, (T, H * dv))
     if not state.is_cuda or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < H * dk * dv:
         raise KernelError("state: must be 32-bit [slots, >= H * dk * dv] with contiguous rows")
-    _call(_lib().bl_recurrent_scan, rule, _p(q), ldq, _p(k), ldk, _p(v), ldv, _p(z), ldz, _p(beta), ldb, _p(coef),
-          ctypes.c_float(z_sign), ctypes.c_float(q_scale), _p(state), ctypes.c_longlong(state.stride(0)), _p(slots), _p(cu_q), R,
+    _call(_lib().bl_recurrent_scan, rule, _p(q), ldq, _p(k), ldk, _p(v), ldv, _p(decay), ldz, _p(beta), ldb,
+          ctypes.c_float(q_scale), _p(state), ctypes.c_longlong(state.stride(0)), _p(slots), _p(cu_q), R,
           _p(out), H, G, dk, dv, _stream())
 
 

@@ -88,11 +88,11 @@ class GatedLinearAttention(_StateMixer):
         proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
         linear(ctx, h, self.w_in, proj, None, EPI_NONE)
         self._joined(proj)
-        z = ctx.empty((T, H * dk), torch.float32)
-        ops.gemm_plain(proj[:, self.off_a:self.off_a + self.rank], self.a2, z, self.a2_bias, EPI_BIAS)
+        decay = ctx.empty((T, H * dk), torch.float32)              # sigmoid(z)^(1 / tau) = exp(-softplus(-z) / tau)
+        ops.gemm_plain_decay(proj[:, self.off_a:self.off_a + self.rank], self.a2, self.a2_bias, self.coef, dk, -1.0, decay)
         o = ctx.empty((T, H * dv), torch.float32)
         ops.recurrent_scan(ops.RULE_GLA, proj[:, :self.off_k], proj[:, self.off_k:self.off_v], proj[:, self.off_v:self.off_g],
-                           z, None, self.coef, -1.0, dk ** -0.5, ctx.state(cache_layer), ctx.slots, ctx.cu_q, o, H, H, dk, dv)
+                           decay, None, dk ** -0.5, ctx.state(cache_layer), ctx.slots, ctx.cu_q, o, H, H, dk, dv)
         y = ctx.empty((T, H * dv))
         ops.head_norm_gate(o, self.norm, proj[:, self.off_g:self.off_a], ops.GATE_SILU, self.eps, y, H, dv)
         linear(ctx, y, self.wo, out, None, epilogue)
@@ -162,13 +162,13 @@ class ChannelDeltaRule(_StateMixer):
         qkv = ctx.empty((T, C), torch.float32)
         ops.conv_silu_unit(proj, self.conv, tail, ctx.slots, ctx.tok_req, ctx.cu_q, qkv, 2 * G, G, dk, dk ** -0.5, self.UNIT_EPS)
         ops.conv_tail_update(proj, self.taps, tail, ctx.slots, ctx.cu_q, C)
-        z = ctx.empty((T, H * dk), torch.float32)
-        ops.gemm_plain(proj[:, self.off_a:self.off_g], self.a2, z, self.dt_bias, EPI_BIAS)
+        decay = ctx.empty((T, H * dk), torch.float32)              # exp(-exp(A_log) * softplus(z + dt_bias))
+        ops.gemm_plain_decay(proj[:, self.off_a:self.off_g], self.a2, self.dt_bias, self.coef, dk, 1.0, decay)
         glog = ctx.empty((T, H * dv), torch.float32)
         ops.gemm_plain(proj[:, self.off_g:self.off_g + self.gate_rank], self.g2, glog, None, EPI_NONE)
         o = ctx.empty((T, H * dv), torch.float32)
-        ops.recurrent_scan(ops.RULE_DELTA, qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], z,
-                           proj[:, self.off_b:self.off_a], self.coef, 1.0, 1.0, state, ctx.slots, ctx.cu_q, o, H, G, dk, dv)
+        ops.recurrent_scan(ops.RULE_DELTA, qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], decay,
+                           proj[:, self.off_b:self.off_a], 1.0, state, ctx.slots, ctx.cu_q, o, H, G, dk, dv)
         y = ctx.empty((T, H * dv))
         ops.head_norm_gate(o, self.norm, glog, ops.GATE_SIGMOID, self.eps, y, H, dv)
         linear(ctx, y, self.wo, out, None, epilogue)

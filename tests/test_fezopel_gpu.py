@@ -386,11 +386,13 @@ def test_recurrence_kernel_in_portions_with_slots_used_again(rule, H, G, dk, dv)
         cat = lambda j, w: torch.cat([p[j].reshape(p[j].shape[0], w) for p in parts]).float().to(DEV).contiguous()
         q, k, v, z, beta = cat(0, G * dk), cat(1, G * dk), cat(2, H * dv), cat(3, H * dk), cat(4, H)
         T = q.shape[0]
+        # the decays come out of the product that makes their pre-activation: here z = z . I + 0
+        decay = torch.empty(T, H * dk, device=DEV)
+        ops.gemm_plain_decay(z, torch.eye(H * dk, device=DEV), None, coef.float().to(DEV), dk, -1.0 if rule == "gla" else 1.0, decay)
         cu = torch.tensor(np.cumsum([0] + [step[r] for r in rids]), dtype=torch.int32, device=DEV)
         out = torch.empty(T, H * dv, device=DEV)
-        ops.recurrent_scan(ops.RULE_GLA if rule == "gla" else ops.RULE_DELTA, q, k, v, z, beta if rule == "delta" else None,
-                           coef.float().to(DEV), -1.0 if rule == "gla" else 1.0, 0.7, state,
-                           torch.tensor([slots[r] for r in rids], dtype=torch.int32, device=DEV), cu, out, H, G, dk, dv)
+        ops.recurrent_scan(ops.RULE_GLA if rule == "gla" else ops.RULE_DELTA, q, k, v, decay, beta if rule == "delta" else None,
+                           0.7, state, torch.tensor([slots[r] for r in rids], dtype=torch.int32, device=DEV), cu, out, H, G, dk, dv)
         o = out.cpu()
         t0 = 0
         for r in rids:
