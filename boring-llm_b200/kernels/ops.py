@@ -334,7 +334,12 @@ def attention_prefill(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles, ou
     _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape); _need(out, "out", torch.bfloat16, (T, H * dh))
     _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
     _need(tiles, "tiles", torch.int32)
-    _call(_lib().bl_attention_prefill_tail, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+    if sinks is None and gate is None:
+        _call(_lib().bl_attention_prefill, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(tiles), tiles.shape[0], _p(out), H, KV, dh, page_size, window,
+          ctypes.c_float(scale), _stream())
+    else:
+        _call(_lib().bl_attention_prefill_tail, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(tiles), tiles.shape[0], _p(out), H, KV, dh, page_size, window,
           ctypes.c_float(scale), *_tail(T, H, sinks, gate), _stream())
 
@@ -353,7 +358,12 @@ def attention_prefill_tc(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles,
     _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape); _need(out, "out", torch.bfloat16, (T, H * dh))
     _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
     _need(tiles, "tiles", torch.int32, (tiles.shape[0], 2))
-    _call(_lib().bl_attention_prefill_tc_tail, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+    if sinks is None and gate is None:
+        _call(_lib().bl_attention_prefill_tc, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(tiles), tiles.shape[0], _p(out), T, n_pages, H, KV, dh, page_size, window,
+          ctypes.c_float(scale), _stream())
+    else:
+        _call(_lib().bl_attention_prefill_tc_tail, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(tiles), tiles.shape[0], _p(out), T, n_pages, H, KV, dh, page_size, window,
           ctypes.c_float(scale), *_tail(T, H, sinks, gate), _stream())
 
@@ -393,7 +403,12 @@ def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_sp
                 raise KernelError("attention_decode: its counters must exist before a capture (run the step once first)")
             # zero once; every launch leaves them at zero again
             counters = _decode_counters[q.device] = torch.zeros(max(n_counters, 4096), dtype=torch.int32, device=q.device)
-    _call(_lib().bl_attention_decode_tail, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+    if sinks is None and gate is None:
+        _call(_lib().bl_attention_decode, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(reqs), n, n_splits, _p(scratch if need else None), _p(counters), _p(out), H, KV, dh,
+          page_size, window, ctypes.c_float(scale), _stream())
+    else:
+        _call(_lib().bl_attention_decode_tail, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(reqs), n, n_splits, _p(scratch if need else None), _p(counters), _p(out), H, KV, dh,
           page_size, window, ctypes.c_float(scale), *_tail(T, H, sinks, gate), _stream())
 
@@ -420,7 +435,12 @@ def attention_decode_tma(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, 
     G = H // KV
     blocks = n * KV * (-(-G // (8 if G <= 8 else 16))) * n_splits
     early = not (n_splits >= DECODE_TMA_LATE_CLUSTER and blocks > _sms())
-    _call(_lib().bl_attention_decode_tma_tail, _p(q), _p(k_cache), _p(v_cache), n_pages, _p(cu_q), _p(ctx_len), _p(block_table),
+    if sinks is None and gate is None:
+        _call(_lib().bl_attention_decode_tma, _p(q), _p(k_cache), _p(v_cache), n_pages, _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(reqs), n, n_splits, _p(out), H, KV, dh, page_size, window, ctypes.c_float(scale),
+          1 if early else 0, _stream())
+    else:
+        _call(_lib().bl_attention_decode_tma_tail, _p(q), _p(k_cache), _p(v_cache), n_pages, _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(reqs), n, n_splits, _p(out), H, KV, dh, page_size, window, ctypes.c_float(scale),
           1 if early else 0, *_tail(T, H, sinks, gate), _stream())
 

@@ -157,3 +157,16 @@ def test_plain_layer_norm_and_forward_shapes():
     np.testing.assert_allclose(y.mean(-1), 0, atol=1e-12)
     np.testing.assert_allclose((y * y).mean(-1), 1, atol=1e-12)
     assert abs(float(pf.gelu_erf(torch.tensor(1.0, dtype=torch.float64))) - 0.5 * (1 + math.erf(1 / math.sqrt(2)))) < 1e-15
+
+
+def test_command_line_lists_the_configuration_and_tensors(tmp_path, capsys):
+    from boring_llm_b200 import FezopelConfig, write_random_model
+    from boring_llm_b200 import cli
+    c = json.loads(json.dumps(CFG))
+    c["layers"][0]["mixer"]["rank"] = 5
+    c["layers"][2]["mixer"].update(rank=3, gate_rank=7)
+    d = str(tmp_path / "m")
+    write_random_model(d, FezopelConfig.from_dict(c), 1)
+    assert cli.main(["--model", d, "--dump-metadata"]) == 0
+    out = capsys.readouterr().out
+    assert "architecture = Fezopel" in out and "tensor l2.mix.q.conv [8, 3] matrix" in out and "tensor l0.dwa [2] norm" in out
