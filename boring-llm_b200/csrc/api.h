@@ -223,6 +223,15 @@ int bl_layernorm(const float* x, const int* row_idx, const void* w, int w_dtype,
 // result, the norm behind the sublayer and the residual sum. gate, gate_bias and b may be null.
 int bl_gated_norm_residual(float* x, const float* sub, const float* gate, int ld_gate, const void* gate_bias, int gb_dtype,
                            const void* w, int w_dtype, const void* b, int b_dtype, int rows, int d, float eps, void* stream);
+// Up to three row-wise steps in one launch, each optional (null pointers leave a step out), for widths that
+// bl_norm_chain_supported takes and 16-byte aligned operands: A (sub != null) x += layer norm(sub * sigmoid(gate +
+// gate_bias)) * w + b; B (streams != null) mix_out = sum_{j < n - 1} coeffs[j] * streams[j] + coeffs[n - 1] * row, the row
+// being stream n - 1 (x); C (w2 != null) y = layer norm(row) * w2 + b2. Bit for bit what the three kernels give.
+int bl_norm_chain_supported(int d, int ld_gate);
+int bl_norm_chain(float* x, const float* sub, const float* gate, int ld_gate, const void* gate_bias, int gb_dtype,
+                  const void* w, int w_dtype, const void* b, int b_dtype, float eps, const float* streams, long long stride,
+                  const void* coeffs, int c_dtype, int n, float* mix_out, const void* w2, int w2_dtype, const void* b2,
+                  int b2_dtype, float eps2, void* y, int y_dtype, int rows, int d, void* stream);
 // out[e] = sum_{j < n} coeffs[j] * streams[j * stride + e], e < count.
 int bl_depth_mix(const float* streams, long long stride, const void* coeffs, int c_dtype, int n, float* out,
                  long long count, void* stream);

@@ -151,6 +151,133 @@ bool rows_fast(int d, const void* a, const void* b2, const void* c, const void* 
            (((uintptr_t)a | (uintptr_t)b2 | (uintptr_t)c | (uintptr_t)w | (uintptr_t)bias) & 15) == 0;
 }
 
+
+// Up to three row-wise steps on one row held in registers, each optional, in the order a layer's end needs them:
+//   A  x += LN(sub * sigmoid(gate + gate_bias)) * w + b            (sub null: the row is x as it stands)
+//   B  mixed = sum_{j < n - 1} c[j] * streams[j] + c[n - 1] * row   (the row is stream n - 1); written to mix_out
+//   C  y = LN(row) * w2 + b2                                         (the norm that reads the row next)
+// Every step does what its own kernel does, in the same order of operations: fusing changes no bit.
+template <typename TY>
+__global__ void __launch_bounds__(ROW_THREADS)
+norm_chain_kernel(float* x, const float* sub, const float* gate, int ld_gate, const void* __restrict__ gb, int gb_dtype,
+                  const void* __restrict__ w, int w_dtype, const void* __restrict__ b, int b_dtype, float eps,
+                  const float* streams, size_t stride, const void* __restrict__ c, int c_dtype, int n, float* mix_out,
+                  const void* __restrict__ w2, int w2_dtype, const void* __restrict__ b2, int b2_dtype, float eps2, TY* y, int d) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    __shared__ float part[4];
+    const int r = blockIdx.x, n4 = d >> 2;
+    float4 v[ROW_VECS];
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)r * d);
+    if (sub) {
+        const float4* src = reinterpret_cast<const float4*>(sub + (size_t)r * d);
+        const float4* g4 = gate ? reinterpret_cast<const float4*>(gate + (size_t)r * ld_gate) : nullptr;
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < ROW_VECS; ++j) {
+            const int i = threadIdx.x + j * ROW_THREADS;
+            if (i < n4) {
+                float4 a = src[i];
+                if (g4) {
+                    float4 g = g4[i];
+                    if (gb) { const float4 t = load4_any(gb, gb_dtype, 4 * i); g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w; }
+                    a.x *= sigmoidf_(g.x); a.y *= sigmoidf_(g.y); a.z *= sigmoidf_(g.z); a.w *= sigmoidf_(g.w);
+                }
+                v[j] = a;
+                s += (a.x + a.y) + (a.z + a.w);
+            }
+        }
+        const float mean = row_block_sum(s, part) / (float)d;
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < ROW_VECS; ++j) {
+            const int i = threadIdx.x + j * ROW_THREADS;
+            if (i < n4) {
+                const float c0 = v[j].x - mean, c1 = v[j].y - mean, c2 = v[j].z - mean, c3 = v[j].w - mean;
+                ss += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+            }
+        }
+        const float inv = 1.0f / sqrtf(row_block_sum(ss, part) / (float)d + eps);
+#pragma unroll
+        for (int j = 0; j < ROW_VECS; ++j) {
+            const int i = threadIdx.x + j * ROW_THREADS;
+            if (i < n4) {
+                const float4 ww = load4_any(w, w_dtype, 4 * i);
+                const float4 bb = b ? load4_any(b, b_dtype, 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 cur = xr[i];
+                cur.x += (v[j].x - mean) * inv * ww.x + bb.x; cur.y += (v[j].y - mean) * inv * ww.y + bb.y;
+                cur.z += (v[j].z - mean) * inv * ww.z + bb.z; cur.w += (v[j].w - mean) * inv * ww.w + bb.w;
+                xr[i] = cur;
+                v[j] = cur;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < ROW_VECS; ++j) {
+            const int i = threadIdx.x + j * ROW_THREADS;
+            if (i < n4) v[j] = xr[i];
+        }
+    }
+    if (streams) {
+        const float4* st4 = reinterpret_cast<const float4*>(streams) + (size_t)r * n4;
+        const size_t stride4 = stride >> 2;
+        float4* mo = reinterpret_cast<float4*>(mix_out + (size_t)r * d);
+#pragma unroll
+        for (int j = 0; j < ROW_VECS; ++j) {
+            const int i = threadIdx.x + j * ROW_THREADS;
+            if (i < n4) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int k = 0; k < n - 1; ++k) {
+                    const float ck = bl_load_any(c, c_dtype, k);
+                    const float4 a = st4[(size_t)k * stride4 + i];
+                    acc.x = fmaf(ck, a.x, acc.x); acc.y = fmaf(ck, a.y, acc.y); acc.z = fmaf(ck, a.z, acc.z); acc.w = fmaf(ck, a.w, acc.w);
+                }
+                const float cl = bl_load_any(c, c_dtype, n - 1);
+                acc.x = fmaf(cl, v[j].x, acc.x); acc.y = fmaf(cl, v[j].y, acc.y); acc.z = fmaf(cl, v[j].z, acc.z); acc.w = fmaf(cl, v[j].w, acc.w);
+                mo[i] = acc;
+                v[j] = acc;
+            }
+        }
+    }
+    if (w2) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < ROW_VECS; ++j) {
+            const int i = threadIdx.x + j * ROW_THREADS;
+            if (i < n4) s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+        }
+        const float mean = row_block_sum(s, part) / (float)d;
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < ROW_VECS; ++j) {
+            const int i = threadIdx.x + j * ROW_THREADS;
+            if (i < n4) {
+                const float c0 = v[j].x - mean, c1 = v[j].y - mean, c2 = v[j].z - mean, c3 = v[j].w - mean;
+                ss += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+            }
+        }
+        const float inv = 1.0f / sqrtf(row_block_sum(ss, part) / (float)d + eps2);
+#pragma unroll
+        for (int j = 0; j < ROW_VECS; ++j) {
+            const int i = threadIdx.x + j * ROW_THREADS;
+            if (i < n4) {
+                const float4 ww = load4_any(w2, w2_dtype, 4 * i);
+                const float4 bb = b2 ? load4_any(b2, b2_dtype, 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float o0 = (v[j].x - mean) * inv * ww.x + bb.x, o1 = (v[j].y - mean) * inv * ww.y + bb.y;
+                const float o2 = (v[j].z - mean) * inv * ww.z + bb.z, o3 = (v[j].w - mean) * inv * ww.w + bb.w;
+                if (sizeof(TY) == 4) {
+                    reinterpret_cast<float4*>(y + (size_t)r * d)[i] = make_float4(o0, o1, o2, o3);
+                } else {
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+                    reinterpret_cast<uint2*>(y + (size_t)r * d)[i] = pk;
+                }
+            }
+        }
+    }
+}
+
 // out[e] = sum_j c[j] * streams[j * stride + e], four values at a time.
 __global__ void depth_mix4_kernel(const float4* streams, size_t stride4, const void* __restrict__ c, int c_dtype, int n,
                                   float4* out, size_t count4) {
@@ -268,5 +395,35 @@ extern "C" int bl_activation(const void* x, int x_dtype, long long ld_x, void* y
     else BL_FAIL("bl_activation: unsupported dtypes %d -> %d", x_dtype, y_dtype);
 #undef BL_GO3
     BL_CHECK_LAUNCH("bl_activation");
+    return 0;
+}
+
+extern "C" int bl_norm_chain_supported(int d, int ld_gate) {
+    return d > 0 && d % 4 == 0 && d <= ROW_THREADS * 4 * ROW_VECS && ld_gate % 4 == 0;
+}
+
+extern "C" int bl_norm_chain(float* x, const float* sub, const float* gate, int ld_gate, const void* gate_bias, int gb_dtype,
+                             const void* w, int w_dtype, const void* b, int b_dtype, float eps, const float* streams,
+                             long long stride, const void* coeffs, int c_dtype, int n, float* mix_out, const void* w2, int w2_dtype,
+                             const void* b2, int b2_dtype, float eps2, void* y, int y_dtype, int rows, int d, void* stream) {
+    if (rows <= 0) return 0;
+    if (!bl_norm_chain_supported(d, gate ? ld_gate : 0)) BL_FAIL("bl_norm_chain: width %d or gate stride %d is not built", d, ld_gate);
+    if ((((uintptr_t)x | (uintptr_t)sub | (uintptr_t)gate | (uintptr_t)gate_bias | (uintptr_t)w | (uintptr_t)b | (uintptr_t)streams |
+          (uintptr_t)mix_out | (uintptr_t)w2 | (uintptr_t)b2 | (uintptr_t)y) & 15) != 0 || stride % 4 != 0)
+        BL_FAIL("bl_norm_chain: every operand must be 16-byte aligned");
+    if (streams && (n < 1 || mix_out == nullptr || coeffs == nullptr)) BL_FAIL("bl_norm_chain: the average needs its streams, weights and a place to go");
+    if (w2 && y == nullptr) BL_FAIL("bl_norm_chain: the norm needs a place to go");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (y_dtype == BL_BF16)
+        BL_CUDA(bl_launch_dependent(norm_chain_kernel<__nv_bfloat16>, dim3(rows), dim3(ROW_THREADS), 0, s, x, sub, gate, ld_gate, gate_bias,
+                                    gb_dtype, w, w_dtype, b, b_dtype, eps, streams, (size_t)stride, coeffs, c_dtype, n, mix_out, w2, w2_dtype,
+                                    b2, b2_dtype, eps2, (__nv_bfloat16*)y, d));
+    else if (y_dtype == BL_F32)
+        BL_CUDA(bl_launch_dependent(norm_chain_kernel<float>, dim3(rows), dim3(ROW_THREADS), 0, s, x, sub, gate, ld_gate, gate_bias,
+                                    gb_dtype, w, w_dtype, b, b_dtype, eps, streams, (size_t)stride, coeffs, c_dtype, n, mix_out, w2, w2_dtype,
+                                    b2, b2_dtype, eps2, (float*)y, d));
+    else
+        BL_FAIL("bl_norm_chain: unknown output dtype %d", y_dtype);
+    BL_CHECK_LAUNCH("bl_norm_chain");
     return 0;
 }

@@ -20,6 +20,7 @@ constexpr int WARPS = 4;
 constexpr int RKMAX = 16;          // rows of a column that one lane holds
 constexpr int MAX_TAPS = 16;
 constexpr int SCAN_SMEM_BYTES = 40 * 1024;
+constexpr int SCAN_VEC_ROWS = 16;  // rows a lane holds in the kernel with 16-byte fetches, where the key size allows
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
@@ -409,6 +410,14 @@ extern "C" int bl_recurrent_scan(int rule, const float* q, int ldq, const float*
     if (rule == BL_RULE_DELTA && beta == nullptr) BL_FAIL("bl_recurrent_scan: the delta rule needs beta");
     int KS = 1;
     while ((dk + KS - 1) / KS > RKMAX) KS *= 2;
+    // The kernel with 16-byte fetches where the key size splits evenly over the lanes. Sixteen rows a lane: eight, with a
+    // butterfly of one more step, were measured and are no faster for one request (64 x 128 heads, 2,048 tokens: 534 us
+    // against 570) and slower where it counts, 128 x 256 heads (752 against 678) and decode steps of 64 requests (115 us
+    // against 67): a token's time is its chain of dependent instructions, not its arithmetic.
+    int rk4 = 0;
+    for (int ks = 1; ks <= 32 && rk4 == 0; ks *= 2)
+        if (dk % (4 * ks) == 0 && dk / ks <= SCAN_VEC_ROWS) { KS = ks; rk4 = dk / (4 * ks); }
+    if (rk4 == 0 && dk % (4 * KS) == 0) rk4 = dk / (4 * KS);
     const int CW = 32 / KS, cols_blk = WARPS * CW;
     const size_t per_token = (size_t)(3 * dk + cols_blk + 4) * sizeof(float);
     int chunk = (int)(SCAN_SMEM_BYTES / (2 * per_token));
@@ -421,8 +430,7 @@ extern "C" int bl_recurrent_scan(int rule, const float* q, int ldq, const float*
     dim3 grid((dv + cols_blk - 1) / cols_blk, H, R);
     cudaStream_t s = (cudaStream_t)stream;
     if (rule != BL_RULE_GLA && rule != BL_RULE_DELTA) BL_FAIL("bl_recurrent_scan: unknown rule %d", rule);
-    if (dk % (4 * KS) == 0) {                          // a lane's rows are whole groups of four
-        const int rk4 = dk / (4 * KS);
+    if (rk4 > 0) {                                     // a lane's rows are whole groups of four
 #define BL_SCAN(D, R4) BL_CUDA(bl_launch_dependent(recurrent_scan_vec_kernel<D, R4>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, \
         z, ldz, beta, ldb, q_scale, state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec))
         const bool dl = rule == BL_RULE_DELTA;

@@ -963,3 +963,45 @@ def linear_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int, fa
     gemm(x, w, sums, None, EPI_NONE, fast=fast)
     activation(sums[:, :N], out, act)
     return sums[:, N:] if rows_w > N else None
+
+
+def norm_chain_supported(x: torch.Tensor, gate: Optional[torch.Tensor]) -> bool:
+    """Whether `norm_chain` takes rows of this width (a multiple of 4, up to 4,096) with this gate (rows 16-byte aligned)."""
+    ld = gate.stride(0) if gate is not None else 0
+    return (x.data_ptr() % 16 == 0 and (gate is None or gate.data_ptr() % 16 == 0)
+            and bool(library.load().bl_norm_chain_supported(x.shape[1], ld)))
+
+
+def norm_chain(x: torch.Tensor, sub: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+               gate_bias: Optional[torch.Tensor] = None, post=None, streams: Optional[torch.Tensor] = None,
+               coeffs: Optional[torch.Tensor] = None, n: int = 0, mix_out: Optional[torch.Tensor] = None, then=None,
+               y: Optional[torch.Tensor] = None) -> None:
+    """Up to three row-wise steps on the 32-bit rows x in one launch (what `gated_norm_residual`, `depth_mix` and
+    `layernorm` do one after the other, bit for bit): with `sub`, x += layer norm(sub * sigmoid(gate + gate_bias)) with
+    the norm `post` = (weight, bias, eps); with `streams` [>= n, T, d] (x being stream n - 1), mix_out = sum_{j < n}
+    coeffs[j] * streams[j]; with `then` = (weight, bias, eps), y = layer norm(that row)."""
+    rows, d = x.shape
+    _need(x, "x", torch.float32)
+    pw = pb = tw = tb = None
+    peps = teps = 0.0
+    ld = 0
+    if sub is not None:
+        _need(sub, "sub", torch.float32, (rows, d))
+        pw, pb, peps = post
+        _need(pw, "post weight", None, (d,))
+        if gate is not None:
+            ld = _rows32(gate, "gate", rows, d)
+    stride = 0
+    if streams is not None:
+        _need(streams, "streams", torch.float32); _need(mix_out, "mix_out", torch.float32, (rows, d)); _need(coeffs, "coeffs")
+        if not (0 < n <= streams.shape[0] and coeffs.numel() >= n and tuple(streams.shape[1:]) == (rows, d)
+                and x.data_ptr() == streams[n - 1].data_ptr()):
+            raise KernelError("norm_chain: x must be stream n - 1 of the streams it is averaged with")
+        stride = streams.stride(0)
+    if then is not None:
+        tw, tb, teps = then
+        _need(tw, "then weight", None, (d,)); _need(y, "y", None, (rows, d))
+    dt = lambda t: _dt(t) if t is not None else 0
+    _call(_lib().bl_norm_chain, _p(x), _p(sub), _p(gate), ld, _p(gate_bias), dt(gate_bias), _p(pw), dt(pw), _p(pb), dt(pb),
+          ctypes.c_float(peps), _p(streams), ctypes.c_longlong(stride), _p(coeffs), dt(coeffs), n, _p(mix_out), _p(tw), dt(tw),
+          _p(tb), dt(tb), ctypes.c_float(teps), _p(y), dt(y) if y is not None else 0, rows, d, _stream())

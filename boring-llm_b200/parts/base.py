@@ -154,6 +154,8 @@ class StepContext:
     memo: dict = field(default_factory=dict)       # what a part works out once per step and its other layers reuse
     next_norm: object = None                       # the norm that reads the residual stream after the part that runs now (or None)
     norm_after_block: object = None                # ... after the block that runs now
+    after_block: object = None                     # what a model wants done with the stream behind the block that runs now
+                                                   # (`parts.depth.AfterBlock`); a block that can fold it into its last kernel does
 
     @property
     def max_q_len(self) -> int:

@@ -9,6 +9,7 @@ from ..kernels import ops
 from ..weights import TensorSpec, MATRIX, BIAS
 from .base import Part, takes_pending_norm, to_device_matrix, to_device_vector
 from .linear import linear, EPI_BIAS, EPI_NONE
+from .norm import LayerNorm
 
 
 class PreNormBlock(Part):
@@ -119,21 +120,51 @@ class GatedSandwichBlock(Part):
         if self._joined is None:                 # the first step: a gate reads what its sublayer reads, so one product serves both
             self._joined = (self.mixer_gate is not None and self.mixer_gate.join_into(self.mixer),
                             self.ffn is not None and self.ffn_gate is not None and self.ffn_gate.join_into(self.ffn))
-        h = self.mixer_norm.forward(ctx, x)
+        # the rows this block's first norm would make may be there already: the kernel that ended the block before made them
+        h = ctx.memo.pop(("normed rows", id(self.mixer_norm)), None)
+        if h is None:
+            h = self.mixer_norm.forward(ctx, x)
+        after, ctx.after_block = ctx.after_block, None     # what the model wants done with the stream behind this block
         sub = ctx.empty(tuple(x.shape), torch.float32)
         self.mixer.mix(ctx, h, sub, cache_layer, write_cache)
-        self._add(ctx, x, sub, h, self.mixer_gate, self.mixer_post_norm, self.mixer if self._joined[0] else None)
-        if self.ffn is not None:
-            h = self.ffn_norm.forward(ctx, x)
-            self.ffn.apply(ctx, h, sub)
-            self._add(ctx, x, sub, h, self.ffn_gate, self.ffn_post_norm, self.ffn if self._joined[1] else None)
+        if self.ffn is None:
+            self._add(ctx, x, sub, h, self.mixer_gate, self.mixer_post_norm, self.mixer if self._joined[0] else None, after=after)
+            return
+        h = self._add(ctx, x, sub, h, self.mixer_gate, self.mixer_post_norm, self.mixer if self._joined[0] else None,
+                      then=self.ffn_norm)
+        self.ffn.apply(ctx, h, sub)
+        self._add(ctx, x, sub, h, self.ffn_gate, self.ffn_post_norm, self.ffn if self._joined[1] else None, after=after)
 
     @staticmethod
-    def _add(ctx, x, sub, h, gate, post, joined_into):
+    def _add(ctx, x, sub, h, gate, post, joined_into, then=None, after=None):
+        """x += post(sub * sigmoid(gate)), then what reads x next, in one launch where the rows allow it: `then` (a norm
+        of this block; its rows are returned) or `after` (the model's: the average over the streams, and the next block's
+        first norm, whose rows are left in the step's memo)."""
         if gate is None:
             g = gb = None
         elif joined_into is not None:
             g, gb = joined_into.joined_out, gate.bias
         else:
             g, gb = gate.logits(ctx, h), None
-        ops.gated_norm_residual(x, sub, g, post.weight, getattr(post, "bias", None), post.eps, gb)
+        chain = isinstance(post, LayerNorm) and ops.norm_chain_supported(x, g)
+        if not chain:
+            ops.gated_norm_residual(x, sub, g, post.weight, getattr(post, "bias", None), post.eps, gb)
+            if after is not None:
+                after.run_unfused(ctx)
+            return then.forward(ctx, x) if then is not None else None
+        pst = (post.weight, post.bias, post.eps)
+        if then is not None:
+            y = ctx.empty(tuple(x.shape))
+            ops.norm_chain(x, sub, g, gb, pst, then=(then.weight, then.bias, then.eps), y=y)
+            return y
+        if after is None:
+            ops.norm_chain(x, sub, g, gb, pst)
+            return None
+        nxt = after.next_norm if isinstance(after.next_norm, LayerNorm) else None
+        y = ctx.empty(tuple(x.shape)) if nxt is not None else None
+        ops.norm_chain(x, sub, g, gb, pst, streams=after.streams, coeffs=after.mix.weight, n=after.mix.n, mix_out=after.out,
+                       then=(nxt.weight, nxt.bias, nxt.eps) if nxt is not None else None, y=y)
+        if nxt is not None:
+            ctx.memo[("normed rows", id(nxt))] = y
+        after.done = True
+        return None

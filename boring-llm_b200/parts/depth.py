@@ -24,3 +24,18 @@ class DepthWeightedAverage(Part):
 
     def forward(self, ctx, streams: torch.Tensor, out: torch.Tensor) -> None:
         ops.depth_mix(streams, self.weight, self.n, out)
+
+
+class AfterBlock:
+    """What a model with a `DepthWeightedAverage` behind every block wants done once a block has left its stream: the
+    average of the streams so far into `out`, and (if the next block begins with a norm) that norm's rows. A block whose
+    last kernel works row by row may do both there and set `done`; else the model calls `run_unfused`."""
+
+    def __init__(self, mix: DepthWeightedAverage, streams: torch.Tensor, out: torch.Tensor, next_norm=None):
+        self.mix, self.streams, self.out, self.next_norm = mix, streams, out, next_norm
+        self.done = False
+
+    def run_unfused(self, ctx) -> None:
+        if not self.done:
+            self.mix.forward(ctx, self.streams, self.out)
+            self.done = True

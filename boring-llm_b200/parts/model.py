@@ -103,9 +103,14 @@ class DecoderModel(Part):
         self.embedding.forward(ctx, out=streams[0])
         streams[1].copy_(streams[0])
         ctx.norm_after_block = None
+        from .depth import AfterBlock
         for i, call in enumerate(self.schedule):
+            nxt = self.blocks[self.schedule[i + 1].block] if i + 1 < n else None
+            after = AfterBlock(self.depth_mix[i], streams, streams[i + 2], getattr(nxt, "mixer_norm", None))
+            ctx.after_block = after                  # a block may fold the average (and the next block's first norm) into its last kernel
             self.blocks[call.block].forward(ctx, streams[i + 1], call.cache, call.write_cache)
-            self.depth_mix[i].forward(ctx, streams, streams[i + 2])
+            ctx.after_block = None
+            after.run_unfused(ctx)
         ctx.memo["streams"] = streams            # for whoever wants to look at the stream after each entry (tests)
         return streams[n + 1]
 

@@ -511,3 +511,35 @@ def test_sinks_and_gates_in_the_tensor_core_attention_kernels(dh, H, G, window):
             ops.attention_decode_tma(qd, kc, vc, cu, cl, tb3, reqs, splits, out, H, window, scale, sg, gd)
             ops.check_status()
             np.testing.assert_allclose(out.float().cpu().numpy(), want[rows].numpy(), err_msg=f"TMA decode, {splits} slices", **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_row_chain_gives_the_bits_of_its_three_kernels(dtype):
+    """Gate + norm + residual, the average over the streams and the next norm in one launch against the three launches."""
+    from boring_llm_b200.kernels import ops
+    T, d, n = 9, 136, 4
+    streams = rnd(n + 1, T, d, seed=1).float().to(DEV)
+    sub, gate = rnd(T, d, seed=2, scale=2.0).float().to(DEV), rnd(T, d + 8, seed=3).float().to(DEV)[:, 8:]
+    gb, w, b = rnd(d, seed=4).float().to(DEV), (rnd(d, seed=5) + 1).float().to(DEV), rnd(d, seed=6).float().to(DEV)
+    w2, b2, c = (rnd(d, seed=7) + 1).float().to(DEV), rnd(d, seed=8).float().to(DEV), rnd(n, seed=9).float().to(DEV)
+    a = streams.clone()
+    ops.gated_norm_residual(a[n - 1], sub, gate, w, b, 1e-5, gb)
+    ops.depth_mix(a, c, n, a[n])
+    ya = torch.empty(T, d, dtype=dtype, device=DEV)
+    ops.layernorm(a[n], w2, b2, 1e-6, ya)
+    f = streams.clone()
+    yf = torch.empty(T, d, dtype=dtype, device=DEV)
+    assert ops.norm_chain_supported(f[n - 1], gate)
+    ops.norm_chain(f[n - 1], sub, gate, gb, (w, b, 1e-5), streams=f, coeffs=c, n=n, mix_out=f[n], then=(w2, b2, 1e-6), y=yf)
+    assert torch.equal(a, f) and torch.equal(ya, yf)
+    # the steps alone: only the residual; the residual and a norm of the same block
+    g = streams.clone()
+    ops.norm_chain(g[n - 1], sub, gate, gb, (w, b, 1e-5))
+    assert torch.equal(g[n - 1], a[n - 1])
+    yg = torch.empty(T, d, dtype=dtype, device=DEV)
+    ops.norm_chain(g[0], sub, None, None, (w, None, 1e-5), then=(w2, None, 1e-6), y=yg)
+    h = streams.clone()
+    ops.gated_norm_residual(h[0], sub, None, w, None, 1e-5)
+    yh = torch.empty(T, d, dtype=dtype, device=DEV)
+    ops.layernorm(h[0], w2, None, 1e-6, yh)
+    assert torch.equal(g[0], h[0]) and torch.equal(yg, yh)
