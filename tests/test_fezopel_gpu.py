@@ -53,8 +53,13 @@ SHAPES = {
         with_ff(att(4, 2, 64, 64, 150, 32, 1000000.0, 0.125), 256),
         with_ff(gla(4, 32, 64, 16.0, 16), 0),
         with_ff(delta(2, 1, 64, 32, 4, 16, 16), 0)]},
+    # nothing is a multiple of 4: every kernel's path for odd widths, products on the plain kernel in both dtypes
+    "S": {"architecture": "Fezopel", "vocab": 77, "width": 50, "norm": {"eps": 1e-6}, "layers": [
+        with_ff(att(3, 3, 10, 6, 7, 6, 50.0, 0.3), 30),
+        with_ff(gla(2, 20, 9, 3.0, 5), 0),
+        with_ff(delta(3, 1, 12, 10, 5, 7, 3), 22)]},
 }
-SEEDS = {"P": 11, "Q": 12, "R": 13}
+SEEDS = {"P": 11, "Q": 12, "R": 13, "S": 14}
 
 
 @pytest.fixture(scope="module")
@@ -101,7 +106,7 @@ BF16_TOL = 6e-2
 
 
 # ---- whole models ---------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("name", ["P", "Q"])
+@pytest.mark.parametrize("name", ["P", "Q", "S"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_prompts_whole_tails_singly_and_portions(folders, name, dtype):
     folder = folders(name, 0.25 if dtype == "float32" else 0.1)
@@ -115,7 +120,7 @@ def test_prompts_whole_tails_singly_and_portions(folders, name, dtype):
                 f"{name} pairs", tol)
 
 
-@pytest.mark.parametrize("name", ["P", "Q"])
+@pytest.mark.parametrize("name", ["P", "Q", "S"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_mixed_batches_reuse_pages_and_slots(folders, name, dtype):
     folder = folders(name, 0.25 if dtype == "float32" else 0.1)
