@@ -362,28 +362,35 @@ def fezopel_config(sizes, n_layers):
                                       "max_position_embeddings": 32768})
 
 
-def kernel_time_line(eng, entries):
-    """One step launched kernel by kernel with a time stamp between every two kernels: microseconds by kernel name
-    (each kernel's own time in place, without the overlap that dependent launches give)."""
+def kernel_time_line(eng, entries, again):
+    """The time of every kernel of one step INSIDE its captured graph: the step is captured with a time stamp between
+    every two kernels, then `again` (the same shape: it replays that graph) runs, and the stamps of the replay give
+    microseconds by kernel name. Stamps serialise neighbours, so the overlap that dependent launches give is not in these
+    figures; the host is (a replay has no host between kernels). The first kernel of the step (the embedding) has no
+    stamp in front of it and is left out."""
+    import torch
     from boring_llm_b200.kernels import ops
     run = eng.runner
-    graphs, run.options.cuda_graphs = run.options.cuda_graphs, False
+    after, run.options.step_graph_after = run.options.step_graph_after, 1
+    run._graphs.clear(); run._step_graphs.clear(); run._step_shapes_seen.clear()      # graphs captured before carry no stamps
     try:
-        before = {e.request_id: (run.cache.get(e.request_id).num_tokens if run.has_request(e.request_id) else 0) for e in entries}
-        run.step(entries)                                     # once untimed (first-use set-up)
-        if not run.cache.state_groups:                        # pages can be rolled back, recurrent state cannot: such a
-            for e in entries:                                 # model's second run continues behind the first
-                run.truncate(e.request_id, before[e.request_id])
         with ops.StepTrace(run.device) as tr:
-            run.step(entries)
+            run.step(entries)                                 # kernel by kernel, then captured: every name twice
+        names = list(tr.names)
+        k = len(names) // 2
+        run.step(again)                                       # the replay
+        torch.cuda.synchronize()
+        t = tr.buf[:len(names) + 1].cpu().tolist()
         out = {}
-        for name, us in tr.durations():
-            k = out.setdefault(name[3:] if name.startswith("bl_") else name, [0, 0.0])
-            k[0] += 1
-            k[1] += us
-        return {n: [c, round(t, 1)] for n, (c, t) in sorted(out.items(), key=lambda kv: -kv[1][1])}
+        for i in range(k + 1, 2 * k):
+            name = names[i]
+            e = out.setdefault(name[3:] if name.startswith("bl_") else name, [0, 0.0])
+            e[0] += 1
+            e[1] += (t[i + 1] - t[i]) / 1000.0
+        return {n: [c, round(us, 1)] for n, (c, us) in sorted(out.items(), key=lambda kv: -kv[1][1])}
     finally:
-        run.options.cuda_graphs = graphs
+        run.options.step_graph_after = after
+        run._graphs.clear(); run._step_graphs.clear(); run._step_shapes_seen.clear()
 
 
 def design_bench(args):
@@ -418,12 +425,16 @@ def design_bench(args):
                                      "launches_per_step": d["launches"] // max(1, min(args.steps, 32)),
                                      "graph_replay_ms": round(d.get("graph_replay_ms", 0.0), 4)}
         vocab = eng.runner.vocab_size
-        m["kernels_prefill_2048_us"] = kernel_time_line(eng, [StepEntry("tl", random_prompt(vocab, PREFILL_TOKENS, 1), [PREFILL_TOKENS - 1])])
+        # a prompt of 2,048 tokens, and a second one of the same shape that replays the first one's graph
+        m["kernels_prefill_2048_us"] = kernel_time_line(
+            eng, [StepEntry("tl0", random_prompt(vocab, PREFILL_TOKENS, 1), [PREFILL_TOKENS - 1])],
+            [StepEntry("tl1", random_prompt(vocab, PREFILL_TOKENS, 2), [PREFILL_TOKENS - 1])])
         for rid in list(eng.runner.cache.live_requests()):
             eng.runner.free_request(rid)
-        for i in range(8):                          # eight requests at a context of 2,000, then one decode step's time line
+        for i in range(8):                          # eight requests at a context of 2,000, then two decode steps
             eng.runner.step([StepEntry(f"d{i}", random_prompt(vocab, 2000, 50 + i), [])])
-        m["kernels_decode_b8_us"] = kernel_time_line(eng, [StepEntry(f"d{i}", [i + 1], [0]) for i in range(8)])
+        m["kernels_decode_b8_us"] = kernel_time_line(eng, [StepEntry(f"d{i}", [i + 1], [0]) for i in range(8)],
+                                                     [StepEntry(f"d{i}", [i + 2], [0]) for i in range(8)])
         for rid in list(eng.runner.cache.live_requests()):
             eng.runner.free_request(rid)
         out["models"][name] = m

@@ -66,6 +66,7 @@ __global__ void depth_mix_kernel(const float* streams, size_t stride, const void
 
 // ---- one block per row, the row in registers (widths that are a multiple of 4, up to ROW_THREADS * 4 * ROW_VECS) ----------
 constexpr int ROW_THREADS = 128, ROW_VECS = 8;
+constexpr int CHAIN_MAX_STREAMS = 512;               // streams the fused average takes (a model of more layers runs the kernels one by one)
 
 __device__ __forceinline__ float row_block_sum(float v, float* part) {
     v = bl_warp_sum(v);
@@ -164,8 +165,11 @@ norm_chain_kernel(float* x, const float* sub, const float* gate, int ld_gate, co
                   const float* streams, size_t stride, const void* __restrict__ c, int c_dtype, int n, float* mix_out,
                   const void* __restrict__ w2, int w2_dtype, const void* __restrict__ b2, int b2_dtype, float eps2, TY* y, int d) {
     bl_pdl_trigger();
-    bl_pdl_wait();
     __shared__ float part[4];
+    __shared__ float cw[CHAIN_MAX_STREAMS];            // the average's weights: model constants, fetched before the wait
+    if (streams)
+        for (int k = threadIdx.x; k < n; k += ROW_THREADS) cw[k] = bl_load_any(c, c_dtype, k);
+    bl_pdl_wait();
     const int r = blockIdx.x, n4 = d >> 2;
     float4 v[ROW_VECS];
     float4* xr = reinterpret_cast<float4*>(x + (size_t)r * d);
@@ -222,20 +226,34 @@ norm_chain_kernel(float* x, const float* sub, const float* gate, int ld_gate, co
         const float4* st4 = reinterpret_cast<const float4*>(streams) + (size_t)r * n4;
         const size_t stride4 = stride >> 2;
         float4* mo = reinterpret_cast<float4*>(mix_out + (size_t)r * d);
+        // stream by stream, a thread's loads of one stream in flight together (the sum of an element stays in ascending j)
+        float4 acc[ROW_VECS];
+#pragma unroll
+        for (int j = 0; j < ROW_VECS; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        __syncthreads();                               // cw is written
+#pragma unroll 4
+        for (int k = 0; k < n - 1; ++k) {
+            const float ck = cw[k];
+            const float4* sk4 = st4 + (size_t)k * stride4;
+#pragma unroll
+            for (int j = 0; j < ROW_VECS; ++j) {
+                const int i = threadIdx.x + j * ROW_THREADS;
+                if (i < n4) {
+                    const float4 a = sk4[i];
+                    acc[j].x = fmaf(ck, a.x, acc[j].x); acc[j].y = fmaf(ck, a.y, acc[j].y);
+                    acc[j].z = fmaf(ck, a.z, acc[j].z); acc[j].w = fmaf(ck, a.w, acc[j].w);
+                }
+            }
+        }
+        const float cl = cw[n - 1];
 #pragma unroll
         for (int j = 0; j < ROW_VECS; ++j) {
             const int i = threadIdx.x + j * ROW_THREADS;
             if (i < n4) {
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int k = 0; k < n - 1; ++k) {
-                    const float ck = bl_load_any(c, c_dtype, k);
-                    const float4 a = st4[(size_t)k * stride4 + i];
-                    acc.x = fmaf(ck, a.x, acc.x); acc.y = fmaf(ck, a.y, acc.y); acc.z = fmaf(ck, a.z, acc.z); acc.w = fmaf(ck, a.w, acc.w);
-                }
-                const float cl = bl_load_any(c, c_dtype, n - 1);
-                acc.x = fmaf(cl, v[j].x, acc.x); acc.y = fmaf(cl, v[j].y, acc.y); acc.z = fmaf(cl, v[j].z, acc.z); acc.w = fmaf(cl, v[j].w, acc.w);
-                mo[i] = acc;
-                v[j] = acc;
+                acc[j].x = fmaf(cl, v[j].x, acc[j].x); acc[j].y = fmaf(cl, v[j].y, acc[j].y);
+                acc[j].z = fmaf(cl, v[j].z, acc[j].z); acc[j].w = fmaf(cl, v[j].w, acc[j].w);
+                mo[i] = acc[j];
+                v[j] = acc[j];
             }
         }
     }
@@ -306,6 +324,33 @@ __global__ void activation_kernel(const TI* x, TO* y, size_t count, int cols, si
         else if (ACT == BL_ACT_GELU_TANH) o = 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
         else o = bl_silu(v);
         bl_store(y + r * ld_y + c, o);
+    }
+}
+
+// The same, four values a thread: 32-bit rows in, cols and both row strides multiples of 4, 16-byte aligned.
+template <typename TO, int ACT>
+__global__ void activation4_kernel(const float* x, TO* y, size_t count4, int cols4, size_t ld_x, size_t ld_y) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count4; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / cols4, c = (e % cols4) * 4;
+        const float4 a = *reinterpret_cast<const float4*>(x + r * ld_x + c);
+        float o[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float v = o[k];
+            if (ACT == BL_ACT_GELU_ERF) o[k] = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+            else if (ACT == BL_ACT_GELU_TANH) o[k] = 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
+            else o[k] = bl_silu(v);
+        }
+        if (sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(y + r * ld_y + c) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+            *reinterpret_cast<uint2*>(y + r * ld_y + c) = pk;
+        }
     }
 }
 
@@ -385,6 +430,17 @@ extern "C" int bl_activation(const void* x, int x_dtype, long long ld_x, void* y
     cudaStream_t s = (cudaStream_t)stream;
     const int g = grid_for((size_t)count, 256);
     if (act != BL_ACT_SILU && act != BL_ACT_GELU_ERF && act != BL_ACT_GELU_TANH) BL_FAIL("bl_activation: unknown activation %d", act);
+    if (x_dtype == BL_F32 && cols % 4 == 0 && ld_x % 4 == 0 && ld_y % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0) {
+        const size_t count4 = (size_t)count / 4;
+        const int g4 = grid_for(count4, 256);
+#define BL_GO4(TO) do { \
+        if (act == BL_ACT_GELU_ERF) BL_CUDA(bl_launch_dependent(activation4_kernel<TO, BL_ACT_GELU_ERF>, dim3(g4), dim3(256), 0, s, (const float*)x, (TO*)y, count4, cols / 4, (size_t)ld_x, (size_t)ld_y)); \
+        else if (act == BL_ACT_GELU_TANH) BL_CUDA(bl_launch_dependent(activation4_kernel<TO, BL_ACT_GELU_TANH>, dim3(g4), dim3(256), 0, s, (const float*)x, (TO*)y, count4, cols / 4, (size_t)ld_x, (size_t)ld_y)); \
+        else BL_CUDA(bl_launch_dependent(activation4_kernel<TO, BL_ACT_SILU>, dim3(g4), dim3(256), 0, s, (const float*)x, (TO*)y, count4, cols / 4, (size_t)ld_x, (size_t)ld_y)); } while (0)
+        if (y_dtype == BL_F32) { BL_GO4(float); BL_CHECK_LAUNCH("bl_activation"); return 0; }
+        if (y_dtype == BL_BF16) { BL_GO4(__nv_bfloat16); BL_CHECK_LAUNCH("bl_activation"); return 0; }
+#undef BL_GO4
+    }
 #define BL_GO3(TI, TO) do { \
         if (act == BL_ACT_GELU_ERF) BL_CUDA(bl_launch_dependent(activation_kernel<TI, TO, BL_ACT_GELU_ERF>, dim3(g), dim3(256), 0, s, (const TI*)x, (TO*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y)); \
         else if (act == BL_ACT_GELU_TANH) BL_CUDA(bl_launch_dependent(activation_kernel<TI, TO, BL_ACT_GELU_TANH>, dim3(g), dim3(256), 0, s, (const TI*)x, (TO*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y)); \
@@ -411,7 +467,8 @@ extern "C" int bl_norm_chain(float* x, const float* sub, const float* gate, int 
     if ((((uintptr_t)x | (uintptr_t)sub | (uintptr_t)gate | (uintptr_t)gate_bias | (uintptr_t)w | (uintptr_t)b | (uintptr_t)streams |
           (uintptr_t)mix_out | (uintptr_t)w2 | (uintptr_t)b2 | (uintptr_t)y) & 15) != 0 || stride % 4 != 0)
         BL_FAIL("bl_norm_chain: every operand must be 16-byte aligned");
-    if (streams && (n < 1 || mix_out == nullptr || coeffs == nullptr)) BL_FAIL("bl_norm_chain: the average needs its streams, weights and a place to go");
+    if (streams && (n < 1 || n > CHAIN_MAX_STREAMS || mix_out == nullptr || coeffs == nullptr))
+        BL_FAIL("bl_norm_chain: the average needs 1..%d streams, weights and a place to go", CHAIN_MAX_STREAMS);
     if (w2 && y == nullptr) BL_FAIL("bl_norm_chain: the norm needs a place to go");
     cudaStream_t s = (cudaStream_t)stream;
     if (y_dtype == BL_BF16)

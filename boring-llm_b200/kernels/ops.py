@@ -965,6 +965,9 @@ def linear_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int, fa
     return sums[:, N:] if rows_w > N else None
 
 
+NORM_CHAIN_MAX_STREAMS = 512      # streams that `norm_chain` averages in its launch
+
+
 def norm_chain_supported(x: torch.Tensor, gate: Optional[torch.Tensor]) -> bool:
     """Whether `norm_chain` takes rows of this width (a multiple of 4, up to 4,096) with this gate (rows 16-byte aligned)."""
     ld = gate.stride(0) if gate is not None else 0

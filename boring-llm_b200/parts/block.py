@@ -160,6 +160,9 @@ class GatedSandwichBlock(Part):
         if after is None:
             ops.norm_chain(x, sub, g, gb, pst)
             return None
+        if after.mix.n > ops.NORM_CHAIN_MAX_STREAMS:             # more layers than the fused average takes
+            ops.norm_chain(x, sub, g, gb, pst)
+            return None
         nxt = after.next_norm if isinstance(after.next_norm, LayerNorm) else None
         y = ctx.empty(tuple(x.shape)) if nxt is not None else None
         ops.norm_chain(x, sub, g, gb, pst, streams=after.streams, coeffs=after.mix.weight, n=after.mix.n, mix_out=after.out,
