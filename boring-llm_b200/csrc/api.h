@@ -263,6 +263,15 @@ int bl_gemm_plain_decay(const float* x, int ldx, const void* w, int w_dtype, con
 int bl_recurrent_scan(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                       const float* a, int lda, const float* beta, int ldb, float q_scale, float* state, long long slot_stride, const int* slots, const int* cu_q, int R,
                       float* out, int H, int G, int dk, int dv, void* stream);
+// The same with long portions cut into nc parts that run side by side (requests with 256 tokens or more in the step;
+// linear attention with key sizes that bl_recurrent_scan_can_split takes): every part first runs from a zero state, then
+// from the request's state folded through the parts before it, and a fold leaves the slot. scratch: R * nc * H * dk *
+// (dv + 1) floats. nc 1: bl_recurrent_scan.
+int bl_recurrent_scan_can_split(int rule, int H, int dk, int dv);   // 0, or the blocks one request's portion runs on
+int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                            const float* a, int lda, const float* beta, int ldb, float q_scale, float* state,
+                            long long slot_stride, const int* slots, const int* cu_q, int R, float* out, int H, int G,
+                            int dk, int dv, int nc, float* scratch, void* stream);
 // y[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[:] * gate(g[t * ld_gate + h * dv + :]) (gate null: none).
 #define BL_GATE_SIGMOID 0
 #define BL_GATE_SILU 1

@@ -20,7 +20,8 @@ constexpr int WARPS = 4;
 constexpr int RKMAX = 16;          // rows of a column that one lane holds
 constexpr int MAX_TAPS = 16;
 constexpr int SCAN_SMEM_BYTES = 40 * 1024;
-constexpr int SCAN_VEC_ROWS = 16;  // rows a lane holds in the kernel with 16-byte fetches, where the key size allows
+constexpr int SCAN_VEC_ROWS = 16;
+constexpr int SCAN_SPLIT_MIN = 256;  // tokens of a request in one step from which its portion is cut into parts that run side by side  // rows a lane holds in the kernel with 16-byte fetches, where the key size allows
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
@@ -184,13 +185,25 @@ __global__ void __launch_bounds__(WARPS * 32)
 recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z, int ldz,
                           const float* beta, int ldb, float q_scale,
                           float* state, size_t slot_stride, const int* __restrict__ slots, const int* __restrict__ cu_q,
-                          float* out, int H, int G, int dk, int dv, int KS, int chunk, int vec) {
+                          float* out, int H, int G, int dk, int dv, int KS, int chunk, int vec,
+                          int nc, int pass, float* part_s, float* part_p) {
     bl_pdl_trigger();
     bl_pdl_wait();
     extern __shared__ __align__(16) float sm[];
     constexpr int RK = RK4 * 4;
-    const int r = blockIdx.z, h = blockIdx.y;
-    const int t0 = cu_q[r], n = cu_q[r + 1] - t0;
+    // A long portion of a request may be cut into nc parts that run side by side (linear attention only: its recurrence is
+    // linear in S with a diagonal transition). pass 1: every part from a ZERO state, leaving its own contribution S_part and
+    // the product P of its decays; pass 2: a part starts from the request's state folded through the parts before it
+    // (S <- P o S + S_part) and writes the outputs; a small kernel then folds all parts into the slot. Short portions
+    // (and nc 1) take one block per (request, head, columns) through pass 0 / 2 as before.
+    const int r = blockIdx.z / nc, part = blockIdx.z % nc, h = blockIdx.y;
+    const int n_all = cu_q[r + 1] - cu_q[r];
+    if (n_all <= 0) return;
+    const bool split = !DELTA && nc > 1 && n_all >= SCAN_SPLIT_MIN;
+    if (!split && (part != 0 || pass == 1)) return;
+    const int part_len = split ? (n_all + nc - 1) / nc : n_all;
+    const int t_first = split ? part * part_len : 0;
+    const int t0 = cu_q[r] + t_first, n = min(n_all - t_first, part_len);
     if (n <= 0) return;
     const int gh = h / (H / G);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -232,9 +245,23 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
     };
 
     issue(0, sm);
-    float st[RK];
+    float st[RK], pr[RK];
 #pragma unroll
-    for (int i = 0; i < RK; ++i) st[i] = col_ok ? S[(size_t)(row0 + i) * dv + c] : 0.f;
+    for (int i = 0; i < RK; ++i) {
+        st[i] = (col_ok && !(split && pass == 1)) ? S[(size_t)(row0 + i) * dv + c] : 0.f;
+        pr[i] = 1.f;
+    }
+    const size_t part_base = ((size_t)r * nc) * H + h;           // + p * H for part p
+    if (split && pass == 2) {
+        for (int p = 0; p < part; ++p) {
+            const float* ps = part_s + (part_base + (size_t)p * H) * dk * dv;
+            const float* pp = part_p + (part_base + (size_t)p * H) * dk;
+#pragma unroll
+            for (int i = 0; i < RK; ++i)
+                st[i] = col_ok ? fmaf(pp[row0 + i], st[i], ps[(size_t)(row0 + i) * dv + c]) : 0.f;
+        }
+    }
+    const bool quiet = split && pass == 1;                       // no outputs yet
     const int v_off = 3 * dk + warp * CW + cc, b_off = 3 * dk + cols_blk;
     const int dk4 = dk >> 2;
 
@@ -259,6 +286,11 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
                 st[i + 1] = fmaf(td[i + 1], st[i + 1], tk[i + 1] * t.v);
                 o0 = fmaf(st[i], tq[i], o0);
                 o1 = fmaf(st[i + 1], tq[i + 1], o1);
+            }
+            if (quiet) {
+#pragma unroll
+                for (int i = 0; i < RK; ++i) pr[i] *= td[i];
+                return;
             }
             o = o0 + o1;
             for (int x = 16; x >= CW; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
@@ -313,9 +345,40 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
         if (tt < m) step(ta, tok0 + tt);
         __syncthreads();                               // the buffer is free for the chunk after next
     }
+    if (split) {
+        if (pass == 1) {
+            float* ps = part_s + (part_base + (size_t)part * H) * dk * dv;
+            float* pp = part_p + (part_base + (size_t)part * H) * dk;
+#pragma unroll
+            for (int i = 0; i < RK; ++i) {
+                if (col_ok) ps[(size_t)(row0 + i) * dv + c] = st[i];
+                if (blockIdx.x == 0 && warp == 0 && cc == 0) pp[row0 + i] = pr[i];
+            }
+        }
+        return;                                        // the slot is written by the fold behind pass 2
+    }
 #pragma unroll
     for (int i = 0; i < RK; ++i)
         if (col_ok) S[(size_t)(row0 + i) * dv + c] = st[i];
+}
+
+// Behind the two passes of a cut portion: the request's state folded through all parts, into its slot.
+__global__ void scan_fold_kernel(float* state, size_t slot_stride, const int* __restrict__ slots, const int* __restrict__ cu_q,
+                                 const float* part_s, const float* part_p, int H, int dk, int dv, int nc) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int r = blockIdx.z, h = blockIdx.y;
+    if (cu_q[r + 1] - cu_q[r] < SCAN_SPLIT_MIN) return;
+    float* S = state + (size_t)slots[r] * slot_stride + (size_t)h * dk * dv;
+    const size_t base = ((size_t)r * nc) * H + h;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= dk * dv) return;
+    const int row = e / dv;
+    float sv = S[e];
+#pragma unroll 4
+    for (int p = 0; p < nc; ++p)
+        sv = fmaf(part_p[(base + (size_t)p * H) * dk + row], sv, part_s[(base + (size_t)p * H) * dk * dv + e]);
+    S[e] = sv;
 }
 
 // y[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[:] * gate(g[t, h, :]); one warp per (token, head).
@@ -403,7 +466,29 @@ __global__ void conv_tail_update_kernel(const float* x, int ld, int n_taps, floa
 extern "C" int bl_recurrent_scan(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                                  const float* z, int ldz, const float* beta, int ldb, float q_scale, float* state, long long slot_stride, const int* slots, const int* cu_q, int R,
                                  float* out, int H, int G, int dk, int dv, void* stream) {
+    return bl_recurrent_scan_parts(rule, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale, state, slot_stride, slots, cu_q, R, out,
+                                   H, G, dk, dv, 1, nullptr, stream);
+}
+
+// Whether bl_recurrent_scan_parts can cut long portions of this rule and key size (else it runs them in one piece):
+// 0, or the blocks that one request's portion (or each of its parts) runs on, H * ceil(dv / columns a block).
+extern "C" int bl_recurrent_scan_can_split(int rule, int H, int dk, int dv) {
+    if (rule != BL_RULE_GLA) return 0;
+    for (int ks = 1; ks <= 32; ks *= 2)
+        if (dk % (4 * ks) == 0 && dk / ks <= SCAN_VEC_ROWS) {
+            const int cols_blk = WARPS * (32 / ks);
+            return H * ((dv + cols_blk - 1) / cols_blk);
+        }
+    return 0;
+}
+
+extern "C" int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                                       const float* z, int ldz, const float* beta, int ldb, float q_scale, float* state,
+                                       long long slot_stride, const int* slots, const int* cu_q, int R, float* out, int H, int G,
+                                       int dk, int dv, int nc, float* scratch, void* stream) {
     if (R <= 0) return 0;
+    if (nc < 1 || (nc > 1 && (scratch == nullptr || !bl_recurrent_scan_can_split(rule, H, dk, dv) || (long long)R * nc > 65535)))
+        BL_FAIL("bl_recurrent_scan_parts: %d parts for rule %d, %d key channels, %d requests", nc, rule, dk, R);
     if (H <= 0 || G <= 0 || H % G != 0 || dk <= 0 || dv <= 0) BL_FAIL("bl_recurrent_scan: bad sizes H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
     if (dk > RKMAX * 32) BL_FAIL("bl_recurrent_scan: %d key channels, at most %d", dk, RKMAX * 32);
     if (R > 65535 || H > 65535) BL_FAIL("bl_recurrent_scan: %d requests or %d heads are too many for one launch", R, H);
@@ -427,23 +512,31 @@ extern "C" int bl_recurrent_scan(int rule, const float* q, int ldq, const float*
     // 16-byte copies where every row of q, k and z starts on a 16-byte boundary
     const int vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldz % 4 == 0 &&
                     (((uintptr_t)q | (uintptr_t)k | (uintptr_t)z) & 15) == 0;
-    dim3 grid((dv + cols_blk - 1) / cols_blk, H, R);
+    dim3 grid((dv + cols_blk - 1) / cols_blk, H, R * nc);
     cudaStream_t s = (cudaStream_t)stream;
     if (rule != BL_RULE_GLA && rule != BL_RULE_DELTA) BL_FAIL("bl_recurrent_scan: unknown rule %d", rule);
     if (rk4 > 0) {                                     // a lane's rows are whole groups of four
-#define BL_SCAN(D, R4) BL_CUDA(bl_launch_dependent(recurrent_scan_vec_kernel<D, R4>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, \
-        z, ldz, beta, ldb, q_scale, state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec))
+        float* part_s = scratch;                                                 // [R, nc, H, dk, dv]
+        float* part_p = scratch ? scratch + (size_t)R * nc * H * dk * dv : nullptr;   // [R, nc, H, dk]
+#define BL_SCAN(D, R4, PASS) BL_CUDA(bl_launch_dependent(recurrent_scan_vec_kernel<D, R4>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, \
+        z, ldz, beta, ldb, q_scale, state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec, nc, PASS, part_s, part_p))
         const bool dl = rule == BL_RULE_DELTA;
-        switch (rk4) {
-            case 1: if (dl) BL_SCAN(true, 1); else BL_SCAN(false, 1); break;
-            case 2: if (dl) BL_SCAN(true, 2); else BL_SCAN(false, 2); break;
-            case 3: if (dl) BL_SCAN(true, 3); else BL_SCAN(false, 3); break;
-            default: if (dl) BL_SCAN(true, 4); else BL_SCAN(false, 4); break;
+        for (int pass = (nc > 1 ? 1 : 2); pass <= 2; ++pass) {
+            switch (rk4) {
+                case 1: if (dl) BL_SCAN(true, 1, pass); else BL_SCAN(false, 1, pass); break;
+                case 2: if (dl) BL_SCAN(true, 2, pass); else BL_SCAN(false, 2, pass); break;
+                case 3: if (dl) BL_SCAN(true, 3, pass); else BL_SCAN(false, 3, pass); break;
+                default: if (dl) BL_SCAN(true, 4, pass); else BL_SCAN(false, 4, pass); break;
+            }
         }
 #undef BL_SCAN
+        if (nc > 1)
+            BL_CUDA(bl_launch_dependent(scan_fold_kernel, dim3((dk * dv + 255) / 256, H, R), dim3(256), 0, s, state, (size_t)slot_stride, slots, cu_q,
+                                        (const float*)part_s, (const float*)part_p, H, dk, dv, nc));
         BL_CHECK_LAUNCH("bl_recurrent_scan");
         return 0;
     }
+    if (nc > 1) BL_FAIL("bl_recurrent_scan_parts: %d key channels cannot be cut into parts", dk);
     if (rule == BL_RULE_GLA)
         BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<false>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale,
             state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec));

@@ -893,13 +893,36 @@ def gemm_plain_decay(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
           _p(coef), group, ctypes.c_float(sign), _stream())
 
 
+SCAN_MAX_PARTS = 16               # most parts a long portion of a request is cut into
+SCAN_PART_MIN_TOKENS = 256        # requests with fewer tokens in a step are walked in one piece (the kernel's own rule)
+SCAN_BLOCKS_PER_SM = 2            # blocks of the scan kernel that an SM holds (its registers)
+
+
+def recurrent_scan_parts(rule: int, H: int, dk: int, dv: int, n_long: int) -> int:
+    """How many parts `recurrent_scan` should cut the portions of a step's `n_long` long requests into (1: none). Cutting
+    runs every token twice, on `parts` times the blocks: time goes as (2 / parts) x rounds of blocks, against 1 x rounds in
+    one piece. It pays while a request's blocks leave most of the device idle (heads x value columns / 32 blocks: 28 for 7
+    heads of 64 x 128, where 10 parts take 0.2 of the time; 128 blocks for 8 heads of 128 x 256, where no cut gains)."""
+    if n_long <= 0:
+        return 1
+    blocks = int(library.load().bl_recurrent_scan_can_split(rule, H, dk, dv)) * n_long
+    if blocks <= 0:
+        return 1
+    room = SCAN_BLOCKS_PER_SM * _sms()
+    rounds = lambda b: -(-b // room)
+    best = min(range(2, SCAN_MAX_PARTS + 1), key=lambda p: (2.0 / p * rounds(blocks * p), p))
+    return best if 2.0 / best * rounds(blocks * best) <= 0.7 * rounds(blocks) else 1
+
+
 def recurrent_scan(rule: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: Optional[torch.Tensor],
                    q_scale: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, out: torch.Tensor,
-                   H: int, G: int, dk: int, dv: int) -> None:
+                   H: int, G: int, dk: int, dv: int, parts: int = 1) -> None:
     """A linear recurrence over a matrix state per head and request (`RULE_GLA`, `RULE_DELTA`; see `bl_recurrent_scan`).
     q, k [T, G * dk], v [T, H * dv], decay [T, H * dk] (in (0, 1], see `gemm_plain_decay`), beta [T, H] (logits): 32-bit
     rows, possibly column ranges of a wider matrix. state: [slots, >= H * dk * dv] 32-bit, the matrix state first in each
-    slot. out [T, H * dv] 32-bit, already times q_scale."""
+    slot. out [T, H * dv] 32-bit, already times q_scale. `parts` > 1 (`recurrent_scan_parts`): portions of 256 tokens and
+    more are cut into that many parts, which run side by side (twice the arithmetic on `parts` times the blocks; the
+    results differ from the walk in one piece by rounding only)."""
     T = out.shape[0]
     R = cu_q.shape[0] - 1
     ldq, ldk, ldv, ldz = (_rows32(q, "q", T, G * dk), _rows32(k, "k", T, G * dk), _rows32(v, "v", T, H * dv),
@@ -909,6 +932,12 @@ def recurrent_scan(rule: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     _need(out, "out", torch.float32, (T, H * dv))
     if not state.is_cuda or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < H * dk * dv:
         raise KernelError("state: must be 32-bit [slots, >= H * dk * dv] with contiguous rows")
+    if parts > 1:
+        scratch = torch.empty(R * parts * H * dk * (dv + 1), dtype=torch.float32, device=out.device)
+        _call(_lib().bl_recurrent_scan_parts, rule, _p(q), ldq, _p(k), ldk, _p(v), ldv, _p(decay), ldz, _p(beta), ldb,
+              ctypes.c_float(q_scale), _p(state), ctypes.c_longlong(state.stride(0)), _p(slots), _p(cu_q), R,
+              _p(out), H, G, dk, dv, parts, _p(scratch), _stream())
+        return
     _call(_lib().bl_recurrent_scan, rule, _p(q), ldq, _p(k), ldk, _p(v), ldv, _p(decay), ldz, _p(beta), ldb,
           ctypes.c_float(q_scale), _p(state), ctypes.c_longlong(state.stride(0)), _p(slots), _p(cu_q), R,
           _p(out), H, G, dk, dv, _stream())

@@ -15,7 +15,7 @@ from ..cache import StateSpec
 from ..kernels import ops
 from ..weights import TensorSpec, MATRIX, BIAS, NORM
 from .attention import Mixer
-from .base import to_device_matrix, to_device_vector
+from .base import StepPlan, to_device_matrix, to_device_vector
 from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
 
 
@@ -82,6 +82,19 @@ class GatedLinearAttention(_StateMixer):
     def cache_spec(self):
         return StateSpec((self.H * self.dk * self.dv,), "float32")
 
+    def _parts(self, q_lens) -> int:
+        n_long = sum(1 for n in q_lens if n >= ops.SCAN_PART_MIN_TOKENS)
+        return ops.recurrent_scan_parts(ops.RULE_GLA, self.H, self.dk, self.dv, n_long) if n_long else 1
+
+    def plan_step(self, q_lens, ctx_lens, filler=None):
+        """Into how many parts this step's long portions are cut (they run side by side): a launch shape, so part of what
+        names a captured step."""
+        parts = self._parts(q_lens)
+        return self._plan_key(), StepPlan(host={"parts": parts}, shape=(parts,))
+
+    def _plan_key(self) -> str:
+        return f"linear attention parts {self.H}x{self.dk}x{self.dv}"         # layers of equal sizes share the plan
+
     def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
         self._check(write_cache)
         T, H, dk, dv = h.shape[0], self.H, self.dk, self.dv
@@ -92,10 +105,18 @@ class GatedLinearAttention(_StateMixer):
         ops.gemm_plain_decay(proj[:, self.off_a:self.off_a + self.rank], self.a2, self.a2_bias, self.coef, dk, -1.0, decay)
         o = ctx.empty((T, H * dv), torch.float32)
         ops.recurrent_scan(ops.RULE_GLA, proj[:, :self.off_k], proj[:, self.off_k:self.off_v], proj[:, self.off_v:self.off_g],
-                           decay, None, dk ** -0.5, ctx.state(cache_layer), ctx.slots, ctx.cu_q, o, H, H, dk, dv)
+                           decay, None, dk ** -0.5, ctx.state(cache_layer), ctx.slots, ctx.cu_q, o, H, H, dk, dv,
+                           parts=self._step_parts(ctx))
         y = ctx.empty((T, H * dv))
         ops.head_norm_gate(o, self.norm, proj[:, self.off_g:self.off_a], ops.GATE_SILU, self.eps, y, H, dv)
         linear(ctx, y, self.wo, out, None, epilogue)
+
+
+    def _step_parts(self, ctx) -> int:
+        plan = ctx.plans.get(self._plan_key())
+        if plan is not None:
+            return plan.host["parts"]
+        return self._parts(ctx.q_lens) if ctx.q_lens else 1       # a step put together without asking the parts
 
 
 class ChannelDeltaRule(_StateMixer):

@@ -555,3 +555,42 @@ def test_the_row_chain_gives_the_bits_of_its_three_kernels(dtype):
     yh = torch.empty(T, d, dtype=dtype, device=DEV)
     ops.layernorm(h[0], w2, None, 1e-6, yh)
     assert torch.equal(g[0], h[0]) and torch.equal(yg, yh)
+
+
+@pytest.mark.parametrize("H,dk,dv", [(2, 16, 24), (1, 64, 40), (3, 48, 8)])
+def test_long_portions_of_linear_attention_cut_into_parts(H, dk, dv):
+    """Three requests in one step, of 700, 256 and 40 tokens (the last is too short to be cut), each from a state that an
+    earlier step left: the parts run side by side and give what the walk in one piece gives, and the slots hold the same
+    states afterwards."""
+    from boring_llm_b200.kernels import ops
+    lens = [700, 256, 40]
+    T = sum(lens)
+    q, k, v = rnd(T, H * dk, seed=1, scale=0.5), rnd(T, H * dk, seed=2, scale=0.5), rnd(T, H * dv, seed=3)
+    a = torch.rand(T, H * dk, generator=torch.Generator().manual_seed(4), dtype=torch.float64) * 0.08 + 0.92
+    start = rnd(3, H * dk * dv, seed=5)
+    cu = torch.tensor(np.cumsum([0] + lens), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, 0, 1], dtype=torch.int32, device=DEV)
+    assert ops.recurrent_scan_parts(ops.RULE_GLA, H, dk, dv, 2) > 1 and ops.recurrent_scan_parts(ops.RULE_DELTA, H, dk, dv, 2) == 1
+    assert ops.recurrent_scan_parts(ops.RULE_GLA, 64, 128, 512, 4) == 1          # enough blocks as it is: a cut would not pay
+    results = []
+    for parts in (1, ops.SCAN_MAX_PARTS, 5):
+        state = torch.zeros(4, H * dk * dv, device=DEV)
+        state[slots.long()] = start.float().to(DEV)
+        out = torch.empty(T, H * dv, device=DEV)
+        ops.recurrent_scan(ops.RULE_GLA, q.float().to(DEV), k.float().to(DEV), v.float().to(DEV), a.float().to(DEV), None, 0.5,
+                           state, slots, cu, out, H, H, dk, dv, parts=parts)
+        results.append((out.cpu(), state.cpu()))
+    # the oracle, with the start states
+    at = 0
+    for i, n in enumerate(lens):
+        S = start[i].reshape(H, dk, dv).clone()
+        want = torch.zeros(n, H, dv, dtype=torch.float64)
+        qq, kk, vv, aa = (x[at:at + n].reshape(n, H, -1) for x in (q, k, v, a))
+        for t in range(n):
+            S = aa[t][:, :, None] * S + kk[t][:, :, None] * vv[t][:, None, :]
+            want[t] = torch.einsum("hkv,hk->hv", S, qq[t] * 0.5)
+        for out, state in results:
+            np.testing.assert_allclose(out[at:at + n].numpy(), want.reshape(n, -1).numpy(), atol=3e-4 * float(want.abs().max()), rtol=3e-4)
+            np.testing.assert_allclose(state[int(slots[i])].numpy(), S.reshape(-1).numpy(), atol=3e-4 * float(S.abs().max()), rtol=3e-4)
+        at += n
+    assert all(torch.equal(st[3], torch.zeros(H * dk * dv)) for _, st in results)
