@@ -594,3 +594,32 @@ def test_long_portions_of_linear_attention_cut_into_parts(H, dk, dv):
             np.testing.assert_allclose(state[int(slots[i])].numpy(), S.reshape(-1).numpy(), atol=3e-4 * float(S.abs().max()), rtol=3e-4)
         at += n
     assert all(torch.equal(st[3], torch.zeros(H * dk * dv)) for _, st in results)
+
+
+@pytest.mark.parametrize("rule", ["gla", "delta"])
+def test_recurrence_inputs_as_odd_column_ranges(rule):
+    """q, k, decays, v and beta as ranges of columns that start at odd offsets of rows of odd length (no 16-byte copies),
+    with a portion long enough to be cut into parts."""
+    from boring_llm_b200.kernels import ops
+    H, G, dk, dv, T = 2, (2 if rule == "gla" else 1), 32, 24, 300
+    wide = lambda cols, seed, scale=1.0: (rnd(T, cols + 7, seed=seed, scale=scale).float().to(DEV))[:, 3:3 + cols]
+    q, k, v, beta = wide(G * dk, 1, 0.4), wide(G * dk, 2, 0.4), wide(H * dv, 3), wide(H, 4)
+    a = (torch.rand(T, H * dk + 5, generator=torch.Generator().manual_seed(5)) * 0.1 + 0.9).to(DEV)[:, 1:1 + H * dk]
+    assert q.stride(0) % 4 != 0 and a.data_ptr() % 16 != 0
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([1], dtype=torch.int32, device=DEV)
+    outs = []
+    for parts in ((1, 7) if rule == "gla" else (1,)):
+        state = torch.zeros(2, H * dk * dv, device=DEV)
+        out = torch.empty(T, H * dv, device=DEV)
+        ops.recurrent_scan(ops.RULE_GLA if rule == "gla" else ops.RULE_DELTA, q, k, v, a, beta if rule == "delta" else None, 1.0,
+                           state, slots, cu, out, H, G, dk, dv, parts=parts)
+        outs.append(out.cpu())
+    d = lambda x, h, w: x.cpu().double().reshape(T, h, w)
+    if rule == "gla":
+        want = pf.gated_linear_recurrence(d(q, H, dk), d(k, H, dk), d(v, H, dv), d(a, H, dk))
+    else:
+        want = pf.delta_recurrence(d(q, G, dk).repeat_interleave(H // G, 1), d(k, G, dk).repeat_interleave(H // G, 1), d(v, H, dv),
+                                   d(a, H, dk), torch.sigmoid(beta.cpu().double()))
+    for out in outs:
+        np.testing.assert_allclose(out.numpy(), want.reshape(T, -1).numpy(), atol=3e-4 * float(want.abs().max()), rtol=3e-4)
