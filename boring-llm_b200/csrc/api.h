@@ -265,8 +265,10 @@ int bl_recurrent_scan(int rule, const float* q, int ldq, const float* k, int ldk
                       float* out, int H, int G, int dk, int dv, void* stream);
 // The same with long portions cut into nc parts that run side by side (requests with 256 tokens or more in the step;
 // linear attention with key sizes that bl_recurrent_scan_can_split takes): every part first runs from a zero state, then
-// from the request's state folded through the parts before it, and a fold leaves the slot. scratch: R * nc * H * dk *
-// (dv + 1) floats. nc 1: bl_recurrent_scan.
+// from the request's state folded through the parts before it, and a fold leaves the slot (the delta rule's fold, a
+// product with the part's key x key transition, runs between the passes). scratch: bl_recurrent_scan_parts_scratch
+// floats. nc 1: bl_recurrent_scan.
+long long bl_recurrent_scan_parts_scratch(int rule, int R, int nc, int H, int dk, int dv);
 int bl_recurrent_scan_can_split(int rule, int H, int dk, int dv);   // 0, or the blocks one request's portion runs on
 int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                             const float* a, int lda, const float* beta, int ldb, float q_scale, float* state,

@@ -186,7 +186,7 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
                           const float* beta, int ldb, float q_scale,
                           float* state, size_t slot_stride, const int* __restrict__ slots, const int* __restrict__ cu_q,
                           float* out, int H, int G, int dk, int dv, int KS, int chunk, int vec,
-                          int nc, int pass, float* part_s, float* part_p) {
+                          int nc, int pass, float* part_s, float* part_p, const float* part_start) {
     bl_pdl_trigger();
     bl_pdl_wait();
     extern __shared__ __align__(16) float sm[];
@@ -194,12 +194,14 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
     // A long portion of a request may be cut into nc parts that run side by side (linear attention only: its recurrence is
     // linear in S with a diagonal transition). pass 1: every part from a ZERO state, leaving its own contribution S_part and
     // the product P of its decays; pass 2: a part starts from the request's state folded through the parts before it
-    // (S <- P o S + S_part) and writes the outputs; a small kernel then folds all parts into the slot. Short portions
+    // (S <- P o S + S_part) and writes the outputs; a small kernel then folds all parts into the slot. The delta rule's
+    // transition is a matrix: its fold (S <- P S + S_part, a small product) runs between the passes, leaves every part's
+    // start state in scratch and the final state in the slot. Short portions
     // (and nc 1) take one block per (request, head, columns) through pass 0 / 2 as before.
     const int r = blockIdx.z / nc, part = blockIdx.z % nc, h = blockIdx.y;
     const int n_all = cu_q[r + 1] - cu_q[r];
     if (n_all <= 0) return;
-    const bool split = !DELTA && nc > 1 && n_all >= SCAN_SPLIT_MIN;
+    const bool split = nc > 1 && n_all >= SCAN_SPLIT_MIN;
     if (!split && (part != 0 || pass == 1)) return;
     const int part_len = split ? (n_all + nc - 1) / nc : n_all;
     const int t_first = split ? part * part_len : 0;
@@ -210,11 +212,15 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
     const int CW = 32 / KS, cols_blk = WARPS * CW;
     const int s = lane / CW, cc = lane % CW;
     const int c = (blockIdx.x * WARPS + warp) * CW + cc;
-    const bool col_ok = c < dv;
+    // The delta rule's transition over a part is a key x key matrix: pass 1 makes it in dk further columns that start as
+    // the identity and see values of zero (column dv + j ends as the part's transition applied to unit vector j).
+    const int n_cols = dv + (DELTA && split && pass == 1 ? dk : 0);
+    const bool col_ok = c < n_cols;
     const int per_tok = 3 * dk + cols_blk + 4;
     const int buf_floats = chunk * per_tok;
     float* S = state + (size_t)slots[r] * slot_stride + (size_t)h * dk * dv;
     const int col0 = blockIdx.x * cols_blk;
+    if (col0 >= n_cols) return;
     const int row0 = s * RK;
 
     auto issue = [&](int base, float* buf) {
@@ -246,13 +252,15 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
 
     issue(0, sm);
     float st[RK], pr[RK];
+    const size_t part_base = ((size_t)r * nc) * H + h;           // + p * H for part p
 #pragma unroll
     for (int i = 0; i < RK; ++i) {
-        st[i] = (col_ok && !(split && pass == 1)) ? S[(size_t)(row0 + i) * dv + c] : 0.f;
+        if (split && pass == 1) st[i] = (DELTA && c >= dv && row0 + i == c - dv) ? 1.f : 0.f;
+        else if (DELTA && split) st[i] = col_ok ? part_start[((part_base + (size_t)part * H) * dk + row0 + i) * dv + c] : 0.f;
+        else st[i] = col_ok ? S[(size_t)(row0 + i) * dv + c] : 0.f;
         pr[i] = 1.f;
     }
-    const size_t part_base = ((size_t)r * nc) * H + h;           // + p * H for part p
-    if (split && pass == 2) {
+    if (!DELTA && split && pass == 2) {
         for (int p = 0; p < part; ++p) {
             const float* ps = part_s + (part_base + (size_t)p * H) * dk * dv;
             const float* pp = part_p + (part_base + (size_t)p * H) * dk;
@@ -315,7 +323,7 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
             for (int i = 0; i < RK; ++i) st[i] = fmaf(tk[i], u, st[i]);
             o = fmaf(kq, u, sq_);
         }
-        if (s == 0 && col_ok) out[tok * H * dv + h * dv + c] = o * q_scale;
+        if (s == 0 && col_ok && !quiet) out[tok * H * dv + h * dv + c] = o * q_scale;
     };
 
     int which = 0;
@@ -346,7 +354,15 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
         __syncthreads();                               // the buffer is free for the chunk after next
     }
     if (split) {
-        if (pass == 1) {
+        if (pass == 1 && DELTA) {
+            float* ps = part_s + (part_base + (size_t)part * H) * dk * dv;
+            float* pm = part_p + (part_base + (size_t)part * H) * dk * dk;      // [row][unit vector]
+#pragma unroll
+            for (int i = 0; i < RK; ++i) {
+                if (c < dv) ps[(size_t)(row0 + i) * dv + c] = st[i];
+                else if (col_ok) pm[(size_t)(row0 + i) * dk + (c - dv)] = st[i];
+            }
+        } else if (pass == 1) {
             float* ps = part_s + (part_base + (size_t)part * H) * dk * dv;
             float* pp = part_p + (part_base + (size_t)part * H) * dk;
 #pragma unroll
@@ -360,6 +376,46 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
 #pragma unroll
     for (int i = 0; i < RK; ++i)
         if (col_ok) S[(size_t)(row0 + i) * dv + c] = st[i];
+}
+
+// Between the two passes of a cut portion of the delta rule: start[0] = the slot's state, start[p + 1] = P_p start[p] +
+// S_part_p (P_p a key x key matrix), the last one into the slot. A block owns FOLD_COLS columns of one (request, head) and
+// keeps the current state's columns in shared memory, two buffers taking turns.
+constexpr int FOLD_COLS = 32, FOLD_MAX_DK = 128;
+__global__ void __launch_bounds__(256)
+scan_fold_matrix_kernel(float* state, size_t slot_stride, const int* __restrict__ slots, const int* __restrict__ cu_q,
+                        const float* part_s, const float* part_pm, float* part_start, int H, int dk, int dv, int nc) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    __shared__ float cur[2][FOLD_MAX_DK][FOLD_COLS];
+    const int r = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * FOLD_COLS;
+    if (cu_q[r + 1] - cu_q[r] < SCAN_SPLIT_MIN) return;
+    float* S = state + (size_t)slots[r] * slot_stride + (size_t)h * dk * dv;
+    const size_t base = ((size_t)r * nc) * H + h;
+    const int col = threadIdx.x % FOLD_COLS, rg = threadIdx.x / FOLD_COLS;      // 8 row groups
+    const bool ok = c0 + col < dv;
+    for (int row = rg; row < dk; row += 8) {
+        const float x = ok ? S[(size_t)row * dv + c0 + col] : 0.f;
+        cur[0][row][col] = x;
+        if (ok) part_start[((base + 0) * dk + row) * dv + c0 + col] = x;
+    }
+    __syncthreads();
+    int w = 0;
+    for (int p = 0; p < nc; ++p, w ^= 1) {
+        const float* pm = part_pm + (base + (size_t)p * H) * dk * dk;
+        const float* ps = part_s + (base + (size_t)p * H) * dk * dv;
+        for (int row = rg; row < dk; row += 8) {
+            float acc = ok ? ps[(size_t)row * dv + c0 + col] : 0.f;
+            const float* prow = pm + (size_t)row * dk;
+            for (int j = 0; j < dk; ++j) acc = fmaf(prow[j], cur[w][j][col], acc);
+            cur[w ^ 1][row][col] = acc;
+            if (ok) {
+                if (p + 1 < nc) part_start[((base + (size_t)(p + 1) * H) * dk + row) * dv + c0 + col] = acc;
+                else S[(size_t)row * dv + c0 + col] = acc;
+            }
+        }
+        __syncthreads();
+    }
 }
 
 // Behind the two passes of a cut portion: the request's state folded through all parts, into its slot.
@@ -471,15 +527,23 @@ extern "C" int bl_recurrent_scan(int rule, const float* q, int ldq, const float*
 }
 
 // Whether bl_recurrent_scan_parts can cut long portions of this rule and key size (else it runs them in one piece):
-// 0, or the blocks that one request's portion (or each of its parts) runs on, H * ceil(dv / columns a block).
+// 0, or the blocks that each part of one request's portion runs on in the first pass, H * ceil(columns / columns a
+// block) (the delta rule's first pass has dk columns more, and its fold takes key sizes up to 128).
 extern "C" int bl_recurrent_scan_can_split(int rule, int H, int dk, int dv) {
-    if (rule != BL_RULE_GLA) return 0;
+    if (rule != BL_RULE_GLA && rule != BL_RULE_DELTA) return 0;
+    if (rule == BL_RULE_DELTA && dk > FOLD_MAX_DK) return 0;
     for (int ks = 1; ks <= 32; ks *= 2)
         if (dk % (4 * ks) == 0 && dk / ks <= SCAN_VEC_ROWS) {
-            const int cols_blk = WARPS * (32 / ks);
-            return H * ((dv + cols_blk - 1) / cols_blk);
+            const int cols_blk = WARPS * (32 / ks), cols = dv + (rule == BL_RULE_DELTA ? dk : 0);
+            return H * ((cols + cols_blk - 1) / cols_blk);
         }
     return 0;
+}
+
+// Floats of scratch that bl_recurrent_scan_parts needs.
+extern "C" long long bl_recurrent_scan_parts_scratch(int rule, int R, int nc, int H, int dk, int dv) {
+    const long long per = rule == BL_RULE_DELTA ? (long long)dk * (2 * dv + dk) : (long long)dk * (dv + 1);
+    return (long long)R * nc * H * per;
 }
 
 extern "C" int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
@@ -513,15 +577,22 @@ extern "C" int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const 
     const int vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldz % 4 == 0 &&
                     (((uintptr_t)q | (uintptr_t)k | (uintptr_t)z) & 15) == 0;
     dim3 grid((dv + cols_blk - 1) / cols_blk, H, R * nc);
+    const dim3 grid_wide((dv + dk + cols_blk - 1) / cols_blk, H, R * nc);     // the delta rule's first pass
     cudaStream_t s = (cudaStream_t)stream;
     if (rule != BL_RULE_GLA && rule != BL_RULE_DELTA) BL_FAIL("bl_recurrent_scan: unknown rule %d", rule);
     if (rk4 > 0) {                                     // a lane's rows are whole groups of four
-        float* part_s = scratch;                                                 // [R, nc, H, dk, dv]
-        float* part_p = scratch ? scratch + (size_t)R * nc * H * dk * dv : nullptr;   // [R, nc, H, dk]
-#define BL_SCAN(D, R4, PASS) BL_CUDA(bl_launch_dependent(recurrent_scan_vec_kernel<D, R4>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, \
-        z, ldz, beta, ldb, q_scale, state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec, nc, PASS, part_s, part_p))
         const bool dl = rule == BL_RULE_DELTA;
+        float* part_s = scratch;                                                 // [R, nc, H, dk, dv]
+        float* part_p = scratch ? scratch + (size_t)R * nc * H * dk * dv : nullptr;   // [R, nc, H, dk] or, delta rule, [R, nc, H, dk, dk]
+        float* part_start = (scratch && dl) ? part_p + (size_t)R * nc * H * dk * dk : nullptr;   // delta rule: [R, nc, H, dk, dv]
+#define BL_SCAN(D, R4, PASS) BL_CUDA(bl_launch_dependent(recurrent_scan_vec_kernel<D, R4>, (D && PASS == 1) ? grid_wide : grid, dim3(WARPS * 32), smem, s, \
+        q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale, state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec, nc, PASS, \
+        part_s, part_p, (const float*)part_start))
         for (int pass = (nc > 1 ? 1 : 2); pass <= 2; ++pass) {
+            if (pass == 2 && nc > 1 && dl)
+                BL_CUDA(bl_launch_dependent(scan_fold_matrix_kernel, dim3((dv + FOLD_COLS - 1) / FOLD_COLS, H, R), dim3(256), 0, s, state,
+                                            (size_t)slot_stride, slots, cu_q, (const float*)part_s, (const float*)part_p, part_start,
+                                            H, dk, dv, nc));
             switch (rk4) {
                 case 1: if (dl) BL_SCAN(true, 1, pass); else BL_SCAN(false, 1, pass); break;
                 case 2: if (dl) BL_SCAN(true, 2, pass); else BL_SCAN(false, 2, pass); break;
@@ -530,7 +601,7 @@ extern "C" int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const 
             }
         }
 #undef BL_SCAN
-        if (nc > 1)
+        if (nc > 1 && !dl)
             BL_CUDA(bl_launch_dependent(scan_fold_kernel, dim3((dk * dv + 255) / 256, H, R), dim3(256), 0, s, state, (size_t)slot_stride, slots, cu_q,
                                         (const float*)part_s, (const float*)part_p, H, dk, dv, nc));
         BL_CHECK_LAUNCH("bl_recurrent_scan");

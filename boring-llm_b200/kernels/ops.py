@@ -902,7 +902,8 @@ def recurrent_scan_parts(rule: int, H: int, dk: int, dv: int, n_long: int) -> in
     """How many parts `recurrent_scan` should cut the portions of a step's `n_long` long requests into (1: none). Cutting
     runs every token twice, on `parts` times the blocks: time goes as (2 / parts) x rounds of blocks, against 1 x rounds in
     one piece. It pays while a request's blocks leave most of the device idle (heads x value columns / 32 blocks: 28 for 7
-    heads of 64 x 128, where 10 parts take 0.2 of the time; 128 blocks for 8 heads of 128 x 256, where no cut gains)."""
+    heads of 64 x 128, where 10 parts take 0.2 of the time; 128 blocks for 8 heads of 128 x 256, where no cut gains). The
+    delta rule's first pass has as many columns more as the key size (its transition over a part is a matrix)."""
     if n_long <= 0:
         return 1
     blocks = int(library.load().bl_recurrent_scan_can_split(rule, H, dk, dv)) * n_long
@@ -933,7 +934,9 @@ def recurrent_scan(rule: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     if not state.is_cuda or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < H * dk * dv:
         raise KernelError("state: must be 32-bit [slots, >= H * dk * dv] with contiguous rows")
     if parts > 1:
-        scratch = torch.empty(R * parts * H * dk * (dv + 1), dtype=torch.float32, device=out.device)
+        lib = _lib()
+        lib.bl_recurrent_scan_parts_scratch.restype = ctypes.c_longlong
+        scratch = torch.empty(int(lib.bl_recurrent_scan_parts_scratch(rule, R, parts, H, dk, dv)), dtype=torch.float32, device=out.device)
         _call(_lib().bl_recurrent_scan_parts, rule, _p(q), ldq, _p(k), ldk, _p(v), ldv, _p(decay), ldz, _p(beta), ldb,
               ctypes.c_float(q_scale), _p(state), ctypes.c_longlong(state.stride(0)), _p(slots), _p(cu_q), R,
               _p(out), H, G, dk, dv, parts, _p(scratch), _stream())

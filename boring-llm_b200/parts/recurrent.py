@@ -35,6 +35,29 @@ class _StateMixer(Mixer):
     def mix(self, ctx, h, out, cache_layer, write_cache=True):
         self._run(ctx, h, out, cache_layer, write_cache, EPI_NONE)
 
+    RULE = None                      # ops.RULE_GLA or ops.RULE_DELTA
+
+    def _parts(self, q_lens) -> int:
+        n_long = sum(1 for n in q_lens if n >= ops.SCAN_PART_MIN_TOKENS)
+        return ops.recurrent_scan_parts(self.RULE, self.H, self.dk, self.dv, n_long) if n_long else 1
+
+    def plan_step(self, q_lens, ctx_lens, filler=None):
+        """Into how many parts this step's long portions are cut (they run side by side): a launch shape, so part of what
+        names a captured step."""
+        parts = self._parts(q_lens)
+        return self._plan_key(), StepPlan(host={"parts": parts}, shape=(parts,))
+
+    def _plan_key(self) -> str:
+        return f"recurrence parts {self.RULE} {self.H}x{self.dk}x{self.dv}"       # layers of equal sizes share the plan
+
+    def _step_parts(self, ctx) -> int:
+        if not ctx.fast:
+            return 1
+        plan = ctx.plans.get(self._plan_key())
+        if plan is not None:
+            return plan.host["parts"]
+        return self._parts(ctx.q_lens) if ctx.q_lens else 1       # a step put together without asking the parts
+
     @staticmethod
     def _check(write_cache):
         if not write_cache:
@@ -50,6 +73,7 @@ class GatedLinearAttention(_StateMixer):
     then each head's o is RMS-normed over its value channels (one plain weight shared by the heads), the heads are
     joined, multiplied by silu(h Wg^T) and projected by Wo. `decay_rank` is the inner size of the decay's two factors
     (None: taken from the tensors when they are loaded)."""
+    RULE = ops.RULE_GLA
 
     def __init__(self, dim: int, n_heads: int, key_dim: int, value_dim: int, tau: float, norm_eps: float,
                  names: Dict[str, str], decay_rank: Optional[int] = None):
@@ -82,19 +106,6 @@ class GatedLinearAttention(_StateMixer):
     def cache_spec(self):
         return StateSpec((self.H * self.dk * self.dv,), "float32")
 
-    def _parts(self, q_lens) -> int:
-        n_long = sum(1 for n in q_lens if n >= ops.SCAN_PART_MIN_TOKENS)
-        return ops.recurrent_scan_parts(ops.RULE_GLA, self.H, self.dk, self.dv, n_long) if n_long else 1
-
-    def plan_step(self, q_lens, ctx_lens, filler=None):
-        """Into how many parts this step's long portions are cut (they run side by side): a launch shape, so part of what
-        names a captured step."""
-        parts = self._parts(q_lens)
-        return self._plan_key(), StepPlan(host={"parts": parts}, shape=(parts,))
-
-    def _plan_key(self) -> str:
-        return f"linear attention parts {self.H}x{self.dk}x{self.dv}"         # layers of equal sizes share the plan
-
     def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
         self._check(write_cache)
         T, H, dk, dv = h.shape[0], self.H, self.dk, self.dv
@@ -112,12 +123,6 @@ class GatedLinearAttention(_StateMixer):
         linear(ctx, y, self.wo, out, None, epilogue)
 
 
-    def _step_parts(self, ctx) -> int:
-        plan = ctx.plans.get(self._plan_key())
-        if plan is not None:
-            return plan.host["parts"]
-        return self._parts(ctx.q_lens) if ctx.q_lens else 1       # a step put together without asking the parts
-
 
 class ChannelDeltaRule(_StateMixer):
     """The gated delta rule with a decay per head AND key channel. q, k (`n_qk_heads` heads of `key_dim`; head h of the
@@ -131,6 +136,7 @@ class ChannelDeltaRule(_StateMixer):
     then o is divided by its root mean square over the value channels, times a plain weight shared by the heads, times
     sigmoid((h G1^T) G2^T), and projected by Wo. The state slot holds S and the convolution's last taps - 1 inputs."""
     UNIT_EPS = 1e-6
+    RULE = ops.RULE_DELTA
 
     def __init__(self, dim: int, n_heads: int, n_qk_heads: int, key_dim: int, value_dim: int, conv_taps: int,
                  norm_eps: float, names: Dict[str, str], decay_rank: Optional[int] = None, gate_rank: Optional[int] = None):
@@ -189,7 +195,8 @@ class ChannelDeltaRule(_StateMixer):
         ops.gemm_plain(proj[:, self.off_g:self.off_g + self.gate_rank], self.g2, glog, None, EPI_NONE)
         o = ctx.empty((T, H * dv), torch.float32)
         ops.recurrent_scan(ops.RULE_DELTA, qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], decay,
-                           proj[:, self.off_b:self.off_a], 1.0, state, ctx.slots, ctx.cu_q, o, H, G, dk, dv)
+                           proj[:, self.off_b:self.off_a], 1.0, state, ctx.slots, ctx.cu_q, o, H, G, dk, dv,
+                           parts=self._step_parts(ctx))
         y = ctx.empty((T, H * dv))
         ops.head_norm_gate(o, self.norm, glog, ops.GATE_SIGMOID, self.eps, y, H, dv)
         linear(ctx, y, self.wo, out, None, epilogue)

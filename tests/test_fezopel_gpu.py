@@ -570,7 +570,8 @@ def test_long_portions_of_linear_attention_cut_into_parts(H, dk, dv):
     start = rnd(3, H * dk * dv, seed=5)
     cu = torch.tensor(np.cumsum([0] + lens), dtype=torch.int32, device=DEV)
     slots = torch.tensor([2, 0, 1], dtype=torch.int32, device=DEV)
-    assert ops.recurrent_scan_parts(ops.RULE_GLA, H, dk, dv, 2) > 1 and ops.recurrent_scan_parts(ops.RULE_DELTA, H, dk, dv, 2) == 1
+    assert ops.recurrent_scan_parts(ops.RULE_GLA, H, dk, dv, 2) > 1 and ops.recurrent_scan_parts(ops.RULE_DELTA, H, dk, dv, 2) > 1
+    assert ops.recurrent_scan_parts(ops.RULE_DELTA, 2, 256, 64, 1) == 1           # the matrix fold takes key sizes up to 128
     assert ops.recurrent_scan_parts(ops.RULE_GLA, 64, 128, 512, 4) == 1          # enough blocks as it is: a cut would not pay
     results = []
     for parts in (1, ops.SCAN_MAX_PARTS, 5):
@@ -609,7 +610,7 @@ def test_recurrence_inputs_as_odd_column_ranges(rule):
     cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
     slots = torch.tensor([1], dtype=torch.int32, device=DEV)
     outs = []
-    for parts in ((1, 7) if rule == "gla" else (1,)):
+    for parts in (1, 7):
         state = torch.zeros(2, H * dk * dv, device=DEV)
         out = torch.empty(T, H * dv, device=DEV)
         ops.recurrent_scan(ops.RULE_GLA if rule == "gla" else ops.RULE_DELTA, q, k, v, a, beta if rule == "delta" else None, 1.0,
@@ -623,3 +624,43 @@ def test_recurrence_inputs_as_odd_column_ranges(rule):
                                    d(a, H, dk), torch.sigmoid(beta.cpu().double()))
     for out in outs:
         np.testing.assert_allclose(out.numpy(), want.reshape(T, -1).numpy(), atol=3e-4 * float(want.abs().max()), rtol=3e-4)
+
+
+@pytest.mark.parametrize("H,G,dk,dv", [(2, 1, 16, 24), (1, 1, 64, 40), (3, 3, 48, 8), (2, 2, 128, 32)])
+def test_long_portions_of_the_delta_rule_cut_into_parts(H, G, dk, dv):
+    """As for linear attention, with the delta rule's transition over a part as a matrix: the walk in one piece, 16 parts
+    and 5 parts against the oracle, from states an earlier step left; a short request in the same step is not cut."""
+    from boring_llm_b200.kernels import ops
+    lens = [600, 300, 30]
+    T = sum(lens)
+    q, k = rnd(T, G, dk, seed=1, scale=0.5), rnd(T, G, dk, seed=2)
+    k = k / k.norm(dim=-1, keepdim=True)
+    v, beta = rnd(T, H, dv, seed=3), rnd(T, H, seed=6)
+    a = torch.rand(T, H, dk, generator=torch.Generator().manual_seed(4), dtype=torch.float64) * 0.08 + 0.92
+    start = rnd(3, H, dk, dv, seed=5)
+    cu = torch.tensor(np.cumsum([0] + lens), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, 0, 1], dtype=torch.int32, device=DEV)
+    f = lambda x: x.reshape(T, -1).float().to(DEV).contiguous()
+    results = []
+    for parts in (1, ops.SCAN_MAX_PARTS, 5):
+        state = torch.zeros(4, H * dk * dv + 3, device=DEV)
+        state[slots.long(), :H * dk * dv] = start.reshape(3, -1).float().to(DEV)
+        out = torch.empty(T, H * dv, device=DEV)
+        ops.recurrent_scan(ops.RULE_DELTA, f(q), f(k), f(v), f(a), f(beta), 0.5, state, slots, cu, out, H, G, dk, dv, parts=parts)
+        results.append((out.cpu(), state.cpu()))
+    rep = H // G
+    at = 0
+    for i, n in enumerate(lens):
+        S = start[i].clone()
+        want = torch.zeros(n, H, dv, dtype=torch.float64)
+        for t in range(at, at + n):
+            kk, qq = k[t].repeat_interleave(rep, 0), q[t].repeat_interleave(rep, 0) * 0.5
+            S = a[t][:, :, None] * S
+            u = torch.sigmoid(beta[t])[:, None] * (v[t] - torch.einsum("hkv,hk->hv", S, kk))
+            S = S + kk[:, :, None] * u[:, None, :]
+            want[t - at] = torch.einsum("hkv,hk->hv", S, qq)
+        for out, state in results:
+            np.testing.assert_allclose(out[at:at + n].numpy(), want.reshape(n, -1).numpy(), atol=5e-4 * float(want.abs().max()), rtol=5e-4)
+            np.testing.assert_allclose(state[int(slots[i]), :H * dk * dv].numpy(), S.reshape(-1).numpy(), atol=5e-4 * float(S.abs().max()), rtol=5e-4)
+        at += n
+    assert all(torch.equal(st[3], torch.zeros(H * dk * dv + 3)) and torch.equal(st[:, H * dk * dv:], torch.zeros(4, 3)) for _, st in results)
