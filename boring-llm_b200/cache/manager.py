@@ -19,11 +19,23 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple, Union
 @dataclass(frozen=True)
 class PagedKVSpec:
     """What a mixer that caches keys and values needs: `window` 0 keeps every key, n > 0 only the
-    last n positions (the query's own included). `v_head_dim` 0: values have the keys' head size."""
+    last n positions (the query's own included). `v_head_dim` 0: values have the keys' head size.
+    `chunk` n > 0: a query sees only the keys of its own run of n positions counted from 0, so the
+    pages before the run of the next position are never read again."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
+    chunk: int = 0
+
+    def first_needed(self, next_pos: int) -> int:
+        """The first key that the query at `next_pos`, or any later one, can still see."""
+        lo = 0
+        if self.window > 0:
+            lo = max(lo, next_pos - self.window + 1)
+        if self.chunk > 0:
+            lo = max(lo, next_pos - next_pos % self.chunk)
+        return lo
 
     @property
     def value_dim(self) -> int:
@@ -131,8 +143,8 @@ class CacheManager:
             if spec is None:
                 continue
             if isinstance(spec, PagedKVSpec):
-                if spec.window < 0:
-                    raise ValueError(f"cache layer {c}: window must not be negative")
+                if spec.window < 0 or spec.chunk < 0:
+                    raise ValueError(f"cache layer {c}: window and chunk must not be negative")
                 for gi, g in enumerate(self.paged_groups):
                     if g.spec == spec:
                         break
@@ -233,10 +245,9 @@ class CacheManager:
             if rc.num_tokens > len(table) * self.page_size:
                 raise CacheError(f"request {request_id!r}: committed past its reserved pages")
         for g, table in zip(self.paged_groups, rc.tables):
-            w = g.spec.window
-            if w <= 0:
+            if g.spec.window <= 0 and g.spec.chunk <= 0:
                 continue
-            first_needed = rc.num_tokens - w + 1
+            first_needed = g.spec.first_needed(rc.num_tokens) if g.spec.chunk > 0 else rc.num_tokens - g.spec.window + 1
             dead = min(len(table), max(0, first_needed) // self.page_size)
             for i in range(dead):
                 if table[i] >= 0:
@@ -252,9 +263,8 @@ class CacheManager:
             raise CacheError(f"truncate({n_keep}) outside 0..{rc.num_tokens}")
         keep_pages = -(-n_keep // self.page_size)
         for g, table in zip(self.paged_groups, rc.tables):
-            w = g.spec.window
-            if w > 0 and n_keep < rc.num_tokens:
-                first_needed = max(0, n_keep - w + 1) // self.page_size
+            if (g.spec.window > 0 or g.spec.chunk > 0) and n_keep < rc.num_tokens:
+                first_needed = (g.spec.first_needed(n_keep) if g.spec.chunk > 0 else max(0, n_keep - g.spec.window + 1)) // self.page_size
                 if any(p < 0 for p in table[first_needed:keep_pages]):
                     raise CacheError("truncate: a window has already given pages of the kept prefix back")
             while len(table) > keep_pages:

@@ -258,6 +258,7 @@ int bl_qk_norm_rope_write(const float* proj, int ld, int off_k, int off_v, const
 // bl_gemm_plain_decay), beta: [T, H] logits (delta rule only), each with its own row stride; out: [T, H * dv] 32-bit.
 #define BL_RULE_GLA 0      // S <- diag(a) S + k v^T; o = S^T (q * q_scale)
 #define BL_RULE_DELTA 1    // S <- diag(a) S; u = sigmoid(beta) (v - S^T k); S <- S + k u^T; o = S^T (q * q_scale)
+#define BL_RULE_BONUS 2    // o = (S^T q + beta v) * q_scale; S <- diag(a) S + k v^T  (the read-out sees the state BEFORE the token's write; beta: a given number per token and head)
 int bl_gemm_plain_decay(const float* x, int ldx, const void* w, int w_dtype, const void* bias, int bias_dtype,
                         float* out, int M, int N, int K, const float* coef, int group, float sign, void* stream);
 int bl_recurrent_scan(int rule, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
@@ -288,6 +289,72 @@ int bl_conv_silu_unit(const float* x, int ld, const float* taps, int n_taps, con
 // The tail of every request with tokens becomes its last n_taps - 1 inputs (after bl_conv_silu_unit has read it).
 int bl_conv_tail_update(const float* x, int ld, int n_taps, float* tail, long long slot_stride, const int* slots,
                         const int* cu_q, int R, int C, void* stream);
+
+// bl_head_norm_gate with two options: w_per_head != 0: w holds H * dv values (a weight per head and channel); den
+// (null: none) [T, H]: o[t, h, :] is divided by den[t, h] before the norm.
+int bl_head_norm_gate_ext(const float* o, const void* w, int w_dtype, int w_per_head, const float* den, const float* gate,
+                          int ld_gate, int gate_kind, void* y, int y_dtype, int T, int H, int dv, float eps, void* stream);
+// The gates of a matrix memory with exponential gating, the tokens of each request in order. proj [T, ld] holds q at
+// off_q and k at off_k (H * dk each) and the gates' pre-activations at off_i and off_f (H each). Per token and head:
+// i = cap tanh((zi + bias_i) / cap), f = log sigmoid(cap tanh((zf + bias_f) / cap)), m' = max(f + m, i), a = e^(f + m - m'),
+// e = e^(i - m'), n' = a n + e k, den = max(|n' . q| q_scale, e^(-m')) + 1e-6. a_out [T, H * dk] (a for every key channel
+// of the head: the decays bl_recurrent_scan reads), k_out [T, H * dk] = e k, den_out [T, H]. n [H, dk] and m [H] are kept
+// in the request's slot at off_n and off_m (floats from the slot's start); a zeroed slot is the start of a sequence.
+int bl_memory_gates(const float* proj, int ld, int off_q, int off_k, int off_i, int off_f, const void* bias_i, int bi_dtype,
+                    const void* bias_f, int bf_dtype, float cap, float q_scale, float* state, long long slot_stride,
+                    long long off_n, long long off_m, const int* slots, const int* cu_q, int R, float* a_out, float* k_out,
+                    float* den_out, int H, int dk, void* stream);
+// out[s, t, :] = x[t, :] + (x'[t, :] - x[t, :]) * mu[s, :], s < n_mix, x' the row of the request's token before; for a
+// step's first token of a request it is prev + slots[r] * slot_stride [d] (bl_conv_tail_update with two taps keeps it).
+int bl_shift_mix(const float* x, int ld, const void* mu, int mu_dtype, int n_mix, const float* prev, long long slot_stride,
+                 const int* slots, const int* tok_req, const int* cu_q, void* out, int out_dtype, int T, int d, void* stream);
+// out[t, h] = sum_c u[h, c] * k[t, h, c] * q[t, h, c] (the beta of BL_RULE_BONUS for a bonus per head and key channel).
+int bl_bonus_dot(const float* q, int ldq, const float* k, int ldk, const void* u, int u_dtype, float* out, int T, int H, int dk,
+                 void* stream);
+
+// bl_qk_norm_rope_write with the norm's scope as an argument: per_head 0: one RMS norm over a token's whole q row (weights
+// [H * dk]) and one over its whole k row ([KV * dk]); per_head != 0: a norm over each head's dk values, the weights [dk]
+// shared by the heads.
+int bl_qk_norm_rope_write_scope(const float* proj, int ld, int off_k, int off_v, const void* q_norm_w, int qw_dtype,
+                                const void* k_norm_w, int kw_dtype, float eps, int per_head, const int* positions,
+                                const int* tok_req, const int* block_table, int max_pages, const float* inv_freq,
+                                int rot_half, int pair_layout, void* q_out, void* k_cache, void* v_cache, int dtype, int T,
+                                int H, int KV, int dk, int dv, int page_size, void* stream);
+// out[m, n] = exp(-exp(u[m, :] . W[n, :] + bias[n])), u = tanh(x) where x_tanh != 0 (x: 32-bit rows ldx apart).
+int bl_gemm_plain_decay_exp(const float* x, int ldx, int x_tanh, const void* w, int w_dtype, const void* bias, int bias_dtype,
+                            float* out, int M, int N, int K, void* stream);
+
+// Layers with the norm behind the sublayer (post_norm.cu): x += LN(s) * w (no bias), s = a, or, with b != null,
+// s = (a / rms(a) * wa + b / rms(b) * wb) / 2 (rms with rms_eps inside the root); y (null: none): the new rows of x in
+// y_dtype as well. bl_cast_rows: y = x in y_dtype. bl_softcap: x = cap * tanh(x / cap) in place.
+int bl_post_norm_residual(float* x, const float* a, const void* wa, int wa_dtype, const float* b, const void* wb, int wb_dtype,
+                          float rms_eps, const void* w, int w_dtype, float eps, void* y, int y_dtype, int rows, int d, void* stream);
+int bl_cast_rows(const float* x, void* y, int y_dtype, long long count, void* stream);
+// out = (a / rms(a) * wa + b / rms(b) * wb) / 2 row by row (32-bit): the mean of two sublayer results, each RMS-normed first.
+int bl_pair_rms_mean(const float* a, const void* wa, int wa_dtype, const float* b, const void* wb, int wb_dtype, float rms_eps,
+                     float* out, int rows, int d, void* stream);
+int bl_softcap(float* x, long long count, float cap, void* stream);
+
+// Attention over the query's own chunk of positions with the heads' softmax weights mixed afterwards (attention_talk.cu).
+// Position i sees j in [i - i % chunk, i] (chunk 0: from 0; window > 0 also j > i - window); score = q . k * scale *
+// head_scale[head] (null: 1). A [T, H, KV, dv] 32-bit: head g's softmax applied to the values of every key/value head;
+// bl_talk_mix: out[t, h, :] = sum_g talk[h, g] A[t, g, kv(h), :].
+int bl_attention_talk_plain(const void* q, const void* k_cache, const void* v_cache, int dtype, const int* tok_req,
+                            const int* cu_q, const int* ctx_len, const int* block_table, int max_pages, float* A, int T, int H,
+                            int KV, int dh, int dv, int page_size, int chunk, int window, float scale, const void* head_scale,
+                            int hs_dtype, void* stream);
+int bl_talk_mix(const float* A, const void* talk, int talk_dtype, void* out, int out_dtype, int T, int H, int KV, int dv, void* stream);
+
+// Routed experts (moe.cu). bl_moe_route: z [T, ldz] 32-bit router logits; s = sigmoid(z), choice = s + correction (null:
+// none); experts in n_groups runs of neighbours, a group's score the sum of its two largest choice scores, the `keep` best
+// groups stay open; ids [T, top] the `top` largest choice scores among them in descending order, wts [T, top] their s.
+// bl_expert_gemm_plain: out[p, :] = epilogue(x[p / x_div, :] . W[ids[p]]^T), W[e] = w + e * expert_stride elements
+// ([N, K], or [2N, K] gate rows then up rows for BL_EPI_SWIGLU). bl_moe_combine: out[t, :] = (add ? out[t, :] : 0) + sum_k wts[t, k] y[t * top + k, :].
+int bl_moe_route(const float* z, int ldz, const void* correction, int corr_dtype, int T, int E, int top, int n_groups, int keep,
+                 int* ids, float* wts, void* stream);
+int bl_expert_gemm_plain(const void* x, int x_dtype, int x_div, const void* w, int w_dtype, long long expert_stride, const int* ids,
+                         void* out, int out_dtype, int P, int N, int K, int epilogue, void* stream);
+int bl_moe_combine(const float* y, const float* wts, float* out, int T, int top, int d, int add, void* stream);
 
 #ifdef __cplusplus
 }

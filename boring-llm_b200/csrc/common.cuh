@@ -16,6 +16,7 @@
 #define BL_EPI_RESIDUAL 2  // out (32-bit, in place) = out + acc
 #define BL_EPI_SWIGLU 3    // out[m, n] = silu(acc_gate[m, n]) * acc_up[m, n]; W holds gate rows then up rows
 #define BL_EPI_DECAY 4     // plain kernel only: out = exp(-coef[n / group] * softplus(sign * (acc + bias[n])))
+#define BL_EPI_DECAY_EXP 5 // plain kernel only: out = exp(-exp(acc + bias[n])), optionally with tanh on x as it is read
 
 // Which two dimensions of a head a rotary position encoding turns together (src/math.br:128-157, its `neox` argument).
 #define BL_PAIRS_HALVES 0        // pair j = (j, j + n_rot / 2)

@@ -15,7 +15,7 @@ template <typename TX, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void* __restrict__ bias,
                   int bias_dtype, TO* __restrict__ out, int M, int N, int K, int ldx,
-                  const float* __restrict__ coef, int group, float sign) {
+                  const float* __restrict__ coef, int group, float sign, int x_tanh = 0) {
     __shared__ float xs[TK][TM + 1];
     __shared__ float ws[TK][TN + 1];
     __shared__ float us[EPI == BL_EPI_SWIGLU ? TK : 1][TN + 1];
@@ -27,7 +27,9 @@ gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void
         for (int i = threadIdx.x; i < TM * TK; i += 256) {
             const int r = i / TK, c = i % TK;
             const int m = m0 + r, k = k0 + c;
-            xs[c][r] = (m < M && k < K) ? bl_load(x + (size_t)m * ldx + k) : 0.f;
+            float xv = (m < M && k < K) ? bl_load(x + (size_t)m * ldx + k) : 0.f;
+            if (EPI == BL_EPI_DECAY_EXP && x_tanh) xv = tanhf(xv);
+            xs[c][r] = xv;
         }
         for (int i = threadIdx.x; i < TN * TK; i += 256) {
             const int r = i / TK, c = i % TK;
@@ -76,6 +78,10 @@ gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void
                 const float u = sign * v;
                 v = expf(-coef[n / group] * (u > 20.f ? u : log1pf(expf(u))));
             }
+            if (EPI == BL_EPI_DECAY_EXP) {             // exp(-exp(acc + bias))
+                if (bias) v += bl_load_any(bias, bias_dtype, n);
+                v = expf(-expf(v));
+            }
             bl_store(dst, v);
         }
     }
@@ -83,16 +89,17 @@ gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void
 
 template <typename TX, typename TW, typename TO>
 int launch_epi(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
-               int M, int N, int K, int ldx, int epi, cudaStream_t s, const float* coef = nullptr, int group = 1, float sign = 1.f) {
+               int M, int N, int K, int ldx, int epi, cudaStream_t s, const float* coef = nullptr, int group = 1, float sign = 1.f, int x_tanh = 0) {
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
 #define BL_GO(E) gemm_plain_kernel<TX, TW, TO, E><<<grid, 256, 0, s>>>( \
-        (const TX*)x, (const TW*)w, bias, bias_dtype, (TO*)out, M, N, K, ldx, coef, group, sign)
+        (const TX*)x, (const TW*)w, bias, bias_dtype, (TO*)out, M, N, K, ldx, coef, group, sign, x_tanh)
     switch (epi) {
         case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
         case BL_EPI_BIAS: BL_GO(BL_EPI_BIAS); break;
         case BL_EPI_RESIDUAL: BL_GO(BL_EPI_RESIDUAL); break;
         case BL_EPI_SWIGLU: BL_GO(BL_EPI_SWIGLU); break;
         case BL_EPI_DECAY: BL_GO(BL_EPI_DECAY); break;
+        case BL_EPI_DECAY_EXP: BL_GO(BL_EPI_DECAY_EXP); break;
         default: BL_FAIL("bl_gemm_plain: unknown epilogue %d", epi);
     }
 #undef BL_GO
@@ -149,4 +156,16 @@ extern "C" int bl_gemm_plain_decay(const float* x, int ldx, const void* w, int w
     if (w_dtype == BL_F32) return launch_epi<float, float, float>(x, w, bias, bias_dtype, out, M, N, K, ldx, BL_EPI_DECAY, s, coef, group, sign);
     if (w_dtype == BL_BF16) return launch_epi<float, __nv_bfloat16, float>(x, w, bias, bias_dtype, out, M, N, K, ldx, BL_EPI_DECAY, s, coef, group, sign);
     BL_FAIL("bl_gemm_plain_decay: unknown matrix dtype %d", w_dtype);
+}
+
+// out[m, n] = exp(-exp(u[m, :] . W[n, :] + bias[n])), u = tanh(x) where x_tanh != 0, else x (32-bit rows ldx apart): decays
+// whose pre-activation is a product in two factors with a tanh between them, as the epilogue of the second factor.
+extern "C" int bl_gemm_plain_decay_exp(const float* x, int ldx, int x_tanh, const void* w, int w_dtype, const void* bias, int bias_dtype,
+                                       float* out, int M, int N, int K, void* stream) {
+    if (M <= 0) return 0;
+    if (N <= 0 || K <= 0 || ldx < K) BL_FAIL("bl_gemm_plain_decay_exp: bad sizes N=%d K=%d ldx=%d", N, K, ldx);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w_dtype == BL_F32) return launch_epi<float, float, float>(x, w, bias, bias_dtype, out, M, N, K, ldx, BL_EPI_DECAY_EXP, s, nullptr, 1, 1.f, x_tanh);
+    if (w_dtype == BL_BF16) return launch_epi<float, __nv_bfloat16, float>(x, w, bias, bias_dtype, out, M, N, K, ldx, BL_EPI_DECAY_EXP, s, nullptr, 1, 1.f, x_tanh);
+    BL_FAIL("bl_gemm_plain_decay_exp: unknown matrix dtype %d", w_dtype);
 }

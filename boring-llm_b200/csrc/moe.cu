@@ -1,0 +1,181 @@
+// Routed experts: the choice of experts per token, matrix products whose rows each use the matrix of their own expert, and
+// the weighted sum of a token's expert results.
+//   scores s = sigmoid(z) (z: the router's 32-bit logits); choice scores c = s + correction; the experts are n_groups equal
+//   runs of neighbours, a group's score is the sum of its two largest choice scores (its only one where groups hold one
+//   expert), only experts of the `keep` best groups can be chosen; the `top` largest choice scores among them are chosen
+//   (ties: the lower index); the weights are the chosen experts' s, as they are.
+// Everything here is a function of the token's row alone: a token's experts, weights and sums do not depend on the batch.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+
+constexpr int WARPS = 4;
+
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+}
+
+// One warp per token. Shared memory: s [E], c [E], group scores [n_groups], kept flags [n_groups].
+__global__ void __launch_bounds__(32)
+moe_route_kernel(const float* __restrict__ z, int ldz, const void* __restrict__ corr, int corr_dtype, int E, int top, int n_groups,
+                 int keep, int* __restrict__ ids, float* __restrict__ wts) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    extern __shared__ float sm[];
+    float* s = sm;
+    float* c = sm + E;
+    float* gs = sm + 2 * E;
+    float* kept = gs + n_groups;
+    const int t = blockIdx.x, lane = threadIdx.x;
+    const int per = E / n_groups;
+    for (int e = lane; e < E; e += 32) {
+        const float v = 1.0f / (1.0f + expf(-z[(size_t)t * ldz + e]));
+        s[e] = v;
+        c[e] = v + (corr ? bl_load_any(corr, corr_dtype, e) : 0.f);
+    }
+    __syncwarp();
+    if (keep < n_groups) {
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;                // the two largest of the group
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = c[e];
+                if (v > a) { b = a; a = v; } else if (v > b) b = v;
+            }
+            gs[g] = per > 1 ? a + b : a;
+            kept[g] = 0.f;
+        }
+        __syncwarp();
+        // the groups that are NOT kept lose their experts: take the best `keep` out, then close the rest
+        for (int n = 0; n < keep; ++n) {
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) if (gs[g] > bv || (gs[g] == bv && g < bi)) { bv = gs[g]; bi = g; }
+            warp_argmax(bv, bi);
+            if (lane == 0 && bi < n_groups) { gs[bi] = -INFINITY; kept[bi] = 1.f; }
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32) if (kept[e / per] == 0.f) c[e] = -INFINITY;
+        __syncwarp();
+    }
+    for (int n = 0; n < top; ++n) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) if (c[e] > bv || (c[e] == bv && e < bi)) { bv = c[e]; bi = e; }
+        warp_argmax(bv, bi);
+        if (bi >= E) bi = 0;                                   // fewer open experts than `top` (refused on the host)
+        if (lane == 0) {
+            ids[(size_t)t * top + n] = bi;
+            wts[(size_t)t * top + n] = s[bi];
+            c[bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+// out[p, n] = epilogue(x[p / x_div, :] . W[ids[p]][n, :]), one warp per output (the lanes over k, a fixed butterfly):
+// the plain product for rows that each have their own matrix. SWIGLU: W[e] holds N gate rows, then N up rows.
+template <typename TX, typename TW, typename TO, int EPI>
+__global__ void __launch_bounds__(WARPS * 32)
+expert_gemm_plain_kernel(const TX* __restrict__ x, int x_div, const TW* __restrict__ w, size_t expert_stride,
+                         const int* __restrict__ ids, TO* __restrict__ out, int P, int N, int K) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * WARPS + (threadIdx.x >> 5);
+    const int p = blockIdx.y;
+    if (n >= N) return;
+    const TX* xr = x + (size_t)(p / x_div) * K;
+    const TW* wr = w + (size_t)ids[p] * expert_stride + (size_t)n * K;
+    float a = 0.f, u = 0.f;
+    for (int k = lane; k < K; k += 32) {
+        const float xv = bl_load(xr + k);
+        a = fmaf(xv, bl_load(wr + k), a);
+        if (EPI == BL_EPI_SWIGLU) u = fmaf(xv, bl_load(wr + (size_t)N * K + k), u);
+    }
+    a = bl_warp_sum(a);
+    if (EPI == BL_EPI_SWIGLU) a = bl_silu(a) * bl_warp_sum(u);
+    if (lane == 0) bl_store(out + (size_t)p * N + n, a);
+}
+
+// out[t, :] = (add ? out[t, :] : 0) + sum_k wts[t, k] * y[t * top + k, :], k ascending.
+__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wts, float* out, int top, int d,
+                                   size_t count, int add) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / d, c = e % d;
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc = fmaf(wts[t * top + k], y[(t * top + k) * d + c], acc);
+        out[e] = add ? out[e] + acc : acc;
+    }
+}
+
+template <typename TX, typename TW, typename TO>
+int launch_expert(const void* x, int x_div, const void* w, size_t stride, const int* ids, void* out, int P, int N, int K, int epi,
+                  cudaStream_t s) {
+    const dim3 grid((N + WARPS - 1) / WARPS, P);
+    if (epi == BL_EPI_NONE)
+        BL_CUDA(bl_launch_dependent(expert_gemm_plain_kernel<TX, TW, TO, BL_EPI_NONE>, grid, dim3(WARPS * 32), 0, s, (const TX*)x, x_div,
+                                    (const TW*)w, stride, ids, (TO*)out, P, N, K));
+    else if (epi == BL_EPI_SWIGLU)
+        BL_CUDA(bl_launch_dependent(expert_gemm_plain_kernel<TX, TW, TO, BL_EPI_SWIGLU>, grid, dim3(WARPS * 32), 0, s, (const TX*)x, x_div,
+                                    (const TW*)w, stride, ids, (TO*)out, P, N, K));
+    else
+        BL_FAIL("bl_expert_gemm_plain: epilogue %d is not built", epi);
+    BL_CHECK_LAUNCH("bl_expert_gemm_plain");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int bl_moe_route(const float* z, int ldz, const void* correction, int corr_dtype, int T, int E, int top, int n_groups,
+                            int keep, int* ids, float* wts, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || top <= 0 || n_groups <= 0 || keep <= 0 || E % n_groups != 0 || keep > n_groups || top > keep * (E / n_groups) || ldz < E)
+        BL_FAIL("bl_moe_route: %d experts in %d groups, %d groups kept, %d chosen", E, n_groups, keep, top);
+    const size_t smem = (size_t)(2 * E + 2 * n_groups) * sizeof(float);
+    if (smem > 48 * 1024) BL_FAIL("bl_moe_route: %d experts are too many for shared memory", E);
+    BL_CUDA(bl_launch_dependent(moe_route_kernel, dim3(T), dim3(32), smem, (cudaStream_t)stream, z, ldz, correction, corr_dtype, E, top,
+                                n_groups, keep, ids, wts));
+    BL_CHECK_LAUNCH("bl_moe_route");
+    return 0;
+}
+
+extern "C" int bl_expert_gemm_plain(const void* x, int x_dtype, int x_div, const void* w, int w_dtype, long long expert_stride,
+                                    const int* ids, void* out, int out_dtype, int P, int N, int K, int epilogue, void* stream) {
+    if (P <= 0) return 0;
+    if (N <= 0 || K <= 0 || x_div <= 0 || P > 65535 * 32) BL_FAIL("bl_expert_gemm_plain: bad sizes P=%d N=%d K=%d", P, N, K);
+    if (P > 65535) {                                          // the grid's y: in slices
+        const size_t xe = x_dtype == BL_F32 ? 4 : 2, oe = out_dtype == BL_F32 ? 4 : 2;
+        const int step = 65535 / x_div * x_div;
+        for (int p0 = 0; p0 < P; p0 += step) {
+            const int n = P - p0 < step ? P - p0 : step;
+            if (bl_expert_gemm_plain((const char*)x + (size_t)(p0 / x_div) * K * xe, x_dtype, x_div, w, w_dtype, expert_stride, ids + p0,
+                                     (char*)out + (size_t)p0 * N * oe, out_dtype, n, N, K, epilogue, stream)) return 1;
+        }
+        return 0;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t st = (size_t)expert_stride;
+    if (x_dtype == BL_F32 && w_dtype == BL_F32 && out_dtype == BL_F32)
+        return launch_expert<float, float, float>(x, x_div, w, st, ids, out, P, N, K, epilogue, s);
+    if (x_dtype == BL_BF16 && w_dtype == BL_BF16 && out_dtype == BL_F32)
+        return launch_expert<__nv_bfloat16, __nv_bfloat16, float>(x, x_div, w, st, ids, out, P, N, K, epilogue, s);
+    if (x_dtype == BL_BF16 && w_dtype == BL_BF16 && out_dtype == BL_BF16)
+        return launch_expert<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(x, x_div, w, st, ids, out, P, N, K, epilogue, s);
+    BL_FAIL("bl_expert_gemm_plain: unsupported dtypes x=%d w=%d out=%d", x_dtype, w_dtype, out_dtype);
+}
+
+extern "C" int bl_moe_combine(const float* y, const float* wts, float* out, int T, int top, int d, int add, void* stream) {
+    if (T <= 0) return 0;
+    if (top <= 0 || d <= 0) BL_FAIL("bl_moe_combine: bad sizes top=%d d=%d", top, d);
+    const size_t count = (size_t)T * d;
+    const int blocks = (int)((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
+    BL_CUDA(bl_launch_dependent(moe_combine_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, y, wts, out, top, d, count, add));
+    BL_CHECK_LAUNCH("bl_moe_combine");
+    return 0;
+}

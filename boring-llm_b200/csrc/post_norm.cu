@@ -1,0 +1,131 @@
+// Row-wise kernels for layers whose norm stands BEHIND the sublayer and whose sublayers read the residual stream itself:
+//   x += LN(s) * w, s = a                                             (one sublayer result)
+//   x += LN(s) * w, s = (RMS(a) * wa + RMS(b) * wb) / 2               (two results side by side, each RMS-normed first)
+// with the stream's rows also handed on in the activation dtype (what the next sublayer's products read), the plain cast
+// of rows, and the soft cap c * tanh(x / c) on logits. Statistics and sums are 32-bit; one warp per row, a lane adds in
+// index order, the warp's sum is a fixed butterfly: a row's result depends on the row alone.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+
+constexpr int ROWS_PER_BLOCK = 4;
+
+template <typename TY>
+__global__ void __launch_bounds__(32 * ROWS_PER_BLOCK)
+post_norm_residual_kernel(float* x, const float* a, const void* __restrict__ wa, int wa_dtype, const float* b,
+                          const void* __restrict__ wb, int wb_dtype, float rms_eps, const void* __restrict__ w, int w_dtype,
+                          float eps, TY* __restrict__ y, int rows, int d) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const float* ar = a + (size_t)r * d;
+    const float* br = b ? b + (size_t)r * d : nullptr;
+    float inv_a = 1.f, inv_b = 1.f;
+    if (br) {
+        float sa = 0.f, sb = 0.f;
+        for (int i = lane; i < d; i += 32) { sa += ar[i] * ar[i]; sb += br[i] * br[i]; }
+        inv_a = 1.0f / sqrtf(bl_warp_sum(sa) / (float)d + rms_eps);
+        inv_b = 1.0f / sqrtf(bl_warp_sum(sb) / (float)d + rms_eps);
+    }
+    auto sub = [&](int i) {
+        return br ? 0.5f * (ar[i] * inv_a * bl_load_any(wa, wa_dtype, i) + br[i] * inv_b * bl_load_any(wb, wb_dtype, i)) : ar[i];
+    };
+    float s = 0.f;
+    for (int i = lane; i < d; i += 32) s += sub(i);
+    const float mean = bl_warp_sum(s) / (float)d;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) { const float c = sub(i) - mean; ss += c * c; }
+    const float inv = 1.0f / sqrtf(bl_warp_sum(ss) / (float)d + eps);
+    float* dst = x + (size_t)r * d;
+    for (int i = lane; i < d; i += 32) {
+        const float v = dst[i] + (sub(i) - mean) * inv * bl_load_any(w, w_dtype, i);
+        dst[i] = v;
+        if (y) bl_store(y + (size_t)r * d + i, v);
+    }
+}
+
+__global__ void __launch_bounds__(32 * ROWS_PER_BLOCK)
+pair_rms_mean_kernel(const float* a, const void* __restrict__ wa, int wa_dtype, const float* b, const void* __restrict__ wb, int wb_dtype,
+                     float rms_eps, float* out, int rows, int d) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const float* ar = a + (size_t)r * d;
+    const float* br = b + (size_t)r * d;
+    float sa = 0.f, sb = 0.f;
+    for (int i = lane; i < d; i += 32) { sa += ar[i] * ar[i]; sb += br[i] * br[i]; }
+    const float inv_a = 1.0f / sqrtf(bl_warp_sum(sa) / (float)d + rms_eps), inv_b = 1.0f / sqrtf(bl_warp_sum(sb) / (float)d + rms_eps);
+    for (int i = lane; i < d; i += 32)
+        out[(size_t)r * d + i] = 0.5f * (ar[i] * inv_a * bl_load_any(wa, wa_dtype, i) + br[i] * inv_b * bl_load_any(wb, wb_dtype, i));
+}
+
+template <typename TY>
+__global__ void cast_rows_kernel(const float* x, TY* y, size_t count) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x) bl_store(y + e, x[e]);
+}
+
+__global__ void softcap_kernel(float* x, size_t count, float cap, float inv_cap) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x)
+        x[e] = cap * tanhf(x[e] * inv_cap);
+}
+
+}  // namespace
+
+extern "C" int bl_post_norm_residual(float* x, const float* a, const void* wa, int wa_dtype, const float* b, const void* wb,
+                                     int wb_dtype, float rms_eps, const void* w, int w_dtype, float eps, void* y, int y_dtype,
+                                     int rows, int d, void* stream) {
+    if (rows <= 0) return 0;
+    if (d <= 0 || a == nullptr || w == nullptr || (b != nullptr && (wa == nullptr || wb == nullptr)))
+        BL_FAIL("bl_post_norm_residual: bad arguments (d=%d)", d);
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), block(32 * ROWS_PER_BLOCK);
+    if (y == nullptr || y_dtype == BL_F32)
+        BL_CUDA(bl_launch_dependent(post_norm_residual_kernel<float>, grid, block, 0, s, x, a, wa, wa_dtype, b, wb, wb_dtype, rms_eps, w,
+                                    w_dtype, eps, (float*)y, rows, d));
+    else if (y_dtype == BL_BF16)
+        BL_CUDA(bl_launch_dependent(post_norm_residual_kernel<__nv_bfloat16>, grid, block, 0, s, x, a, wa, wa_dtype, b, wb, wb_dtype, rms_eps,
+                                    w, w_dtype, eps, (__nv_bfloat16*)y, rows, d));
+    else
+        BL_FAIL("bl_post_norm_residual: unknown output dtype %d", y_dtype);
+    BL_CHECK_LAUNCH("bl_post_norm_residual");
+    return 0;
+}
+
+extern "C" int bl_pair_rms_mean(const float* a, const void* wa, int wa_dtype, const float* b, const void* wb, int wb_dtype, float rms_eps,
+                                float* out, int rows, int d, void* stream) {
+    if (rows <= 0) return 0;
+    if (d <= 0 || !a || !b || !wa || !wb) BL_FAIL("bl_pair_rms_mean: bad arguments (d=%d)", d);
+    BL_CUDA(bl_launch_dependent(pair_rms_mean_kernel, dim3((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), dim3(32 * ROWS_PER_BLOCK), 0,
+                                (cudaStream_t)stream, a, wa, wa_dtype, b, wb, wb_dtype, rms_eps, out, rows, d));
+    BL_CHECK_LAUNCH("bl_pair_rms_mean");
+    return 0;
+}
+
+extern "C" int bl_cast_rows(const float* x, void* y, int y_dtype, long long count, void* stream) {
+    if (count <= 0) return 0;
+    const int blocks = (int)((count + 1023) / 1024 < 2048 ? (count + 1023) / 1024 : 2048);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (y_dtype == BL_BF16) BL_CUDA(bl_launch_dependent(cast_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, x, (__nv_bfloat16*)y, (size_t)count));
+    else if (y_dtype == BL_F32) BL_CUDA(bl_launch_dependent(cast_rows_kernel<float>, dim3(blocks), dim3(256), 0, s, x, (float*)y, (size_t)count));
+    else BL_FAIL("bl_cast_rows: unknown output dtype %d", y_dtype);
+    BL_CHECK_LAUNCH("bl_cast_rows");
+    return 0;
+}
+
+extern "C" int bl_softcap(float* x, long long count, float cap, void* stream) {
+    if (count <= 0) return 0;
+    if (!(cap > 0.f)) BL_FAIL("bl_softcap: the cap must be positive, got %g", cap);
+    const int blocks = (int)((count + 1023) / 1024 < 2048 ? (count + 1023) / 1024 : 2048);
+    BL_CUDA(bl_launch_dependent(softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, (size_t)count, cap, 1.0f / cap));
+    BL_CHECK_LAUNCH("bl_softcap");
+    return 0;
+}

@@ -1,8 +1,10 @@
 // Linear recurrences with a matrix state per head, S [key channels, value channels], carried per request in a state
 // slot, for prompts' portions and single decoded tokens alike (a request's tokens are cu_q[r] .. cu_q[r + 1] - 1 of
-// the batch; a request without tokens is left alone). Two rules share one kernel:
+// the batch; a request without tokens is left alone). Three rules share one kernel:
 //   gated linear attention   S <- diag(a) S + k v^T;                                   o = S^T q
 //   gated delta rule         S <- diag(a) S;  u = beta (v - S^T k);  S <- S + k u^T;   o = S^T q
+//   read-out before the write, with a bonus for the current token
+//                            o = S^T q + b v;  S <- diag(a) S + k v^T                  (b per token and head, given)
 // with a decay per key channel a, given per token, head and channel (the product that makes its pre-activation z turns it
 // into exp(-coef[head] * softplus(sign * z)); sign -1, coef 1 / tau gives sigmoid(z)^(1 / tau)). State, decays, gates and
 // all sums are 32-bit. The columns of S are
@@ -37,7 +39,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // The tokens of a request pass through shared memory in chunks of `chunk` tokens, two buffers taking turns: while the
 // warps walk one chunk, the next one's q, k, z, v and beta are on their way (cp.async); when it has arrived the block
 // squashes beta in place, once for all its columns.
-template <bool DELTA>
+template <int RULE>
 __global__ void __launch_bounds__(WARPS * 32)
 recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z, int ldz,
                       const float* beta, int ldb, float q_scale,
@@ -46,6 +48,7 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
     bl_pdl_trigger();
     bl_pdl_wait();
     extern __shared__ __align__(16) float sm[];
+    constexpr bool DELTA = RULE == BL_RULE_DELTA, BONUS = RULE == BL_RULE_BONUS;
     const int r = blockIdx.z, h = blockIdx.y;
     const int t0 = cu_q[r], n = cu_q[r + 1] - t0;
     if (n <= 0) return;
@@ -82,7 +85,7 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
                 if (col0 + j < dv) cp_async4(dst + 3 * dk + j, gv + j);
                 else dst[3 * dk + j] = 0.f;
             }
-            if (DELTA && lane == 0) cp_async4(dst + 3 * dk + cols_blk, beta + tok * ldb + h);
+            if ((DELTA || BONUS) && lane == 0) cp_async4(dst + 3 * dk + cols_blk, beta + tok * ldb + h);
         }
         cp_async_commit();
     };
@@ -124,7 +127,7 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
                 fd[i] = pq[2 * dk + rr];
             }
             fv = pq[3 * dk + warp * CW + cc];
-            if (DELTA) fb = pq[3 * dk + cols_blk];
+            if (DELTA || BONUS) fb = pq[3 * dk + cols_blk];
         };
         fetch(0, cq, ck, cd, cv, cb);
         for (int tt = 0; tt < m; ++tt) {
@@ -134,13 +137,14 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
                 float o0 = 0.f, o1 = 0.f;
 #pragma unroll
                 for (int i = 0; i < RKMAX; i += 2) {
+                    if (BONUS) { o0 = fmaf(st[i], cq[i], o0); o1 = fmaf(st[i + 1], cq[i + 1], o1); }   // the state before the write
                     st[i] = fmaf(cd[i], st[i], ck[i] * cv);
                     st[i + 1] = fmaf(cd[i + 1], st[i + 1], ck[i + 1] * cv);
-                    o0 = fmaf(st[i], cq[i], o0);
-                    o1 = fmaf(st[i + 1], cq[i + 1], o1);
+                    if (!BONUS) { o0 = fmaf(st[i], cq[i], o0); o1 = fmaf(st[i + 1], cq[i + 1], o1); }
                 }
                 o = o0 + o1;
                 for (int x = 16; x >= CW; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+                if (BONUS) o = fmaf(cb, cv, o);
             } else {
                 float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f, kq0 = 0.f, kq1 = 0.f;
 #pragma unroll
@@ -180,7 +184,7 @@ recurrent_scan_kernel(const float* q, int ldq, const float* k, int ldk, const fl
 // so a token's q, k and decays reach its registers as 16-byte loads at fixed offsets, two tokens' registers take turns
 // (no copies), and the dot products run in two chains. A warp has no other warp on its scheduler to hide latencies
 // behind (a request gives H * dv / (WARPS * CW) blocks): what counts is the number of instructions per token.
-template <bool DELTA, int RK4>
+template <int RULE, int RK4>
 __global__ void __launch_bounds__(WARPS * 32)
 recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z, int ldz,
                           const float* beta, int ldb, float q_scale,
@@ -190,6 +194,7 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
     bl_pdl_trigger();
     bl_pdl_wait();
     extern __shared__ __align__(16) float sm[];
+    constexpr bool DELTA = RULE == BL_RULE_DELTA, BONUS = RULE == BL_RULE_BONUS;
     constexpr int RK = RK4 * 4;
     // A long portion of a request may be cut into nc parts that run side by side (linear attention only: its recurrence is
     // linear in S with a diagonal transition). pass 1: every part from a ZERO state, leaving its own contribution S_part and
@@ -245,7 +250,7 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
                 if (col0 + j < dv) cp_async4(dst + 3 * dk + j, gv + j);
                 else dst[3 * dk + j] = 0.f;
             }
-            if (DELTA && lane == 0) cp_async4(dst + 3 * dk + cols_blk, beta + tok * ldb + h);
+            if ((DELTA || BONUS) && lane == 0) cp_async4(dst + 3 * dk + cols_blk, beta + tok * ldb + h);
         }
         cp_async_commit();
     };
@@ -279,7 +284,7 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
 #pragma unroll
         for (int j = 0; j < RK4; ++j) { t.q[j] = p4[j]; t.k[j] = p4[dk4 + j]; t.d[j] = p4[2 * dk4 + j]; }
         t.v = tokp[v_off];
-        t.b = DELTA ? tokp[b_off] : 0.f;
+        t.b = (DELTA || BONUS) ? tokp[b_off] : 0.f;
     };
     auto step = [&](const Tok& t, size_t tok) {
         const float* tq = reinterpret_cast<const float*>(t.q);
@@ -290,10 +295,10 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
             float o0 = 0.f, o1 = 0.f;
 #pragma unroll
             for (int i = 0; i < RK; i += 2) {
+                if (BONUS) { o0 = fmaf(st[i], tq[i], o0); o1 = fmaf(st[i + 1], tq[i + 1], o1); }       // the state before the write
                 st[i] = fmaf(td[i], st[i], tk[i] * t.v);
                 st[i + 1] = fmaf(td[i + 1], st[i + 1], tk[i + 1] * t.v);
-                o0 = fmaf(st[i], tq[i], o0);
-                o1 = fmaf(st[i + 1], tq[i + 1], o1);
+                if (!BONUS) { o0 = fmaf(st[i], tq[i], o0); o1 = fmaf(st[i + 1], tq[i + 1], o1); }
             }
             if (quiet) {
 #pragma unroll
@@ -302,6 +307,7 @@ recurrent_scan_vec_kernel(const float* q, int ldq, const float* k, int ldk, cons
             }
             o = o0 + o1;
             for (int x = 16; x >= CW; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+            if (BONUS) o = fmaf(t.b, t.v, o);
         } else {
             float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f, kq0 = 0.f, kq1 = 0.f;
 #pragma unroll
@@ -437,11 +443,12 @@ __global__ void scan_fold_kernel(float* state, size_t slot_stride, const int* __
     S[e] = sv;
 }
 
-// y[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[:] * gate(g[t, h, :]); one warp per (token, head).
+// y[t, h, :] = u / sqrt(mean(u^2) + eps) * w * gate(g[t, h, :]), u = o[t, h, :] / den[t, h] (den null: u = o); w is one
+// vector of dv values shared by the heads, or (w_per_head) H * dv values; one warp per (token, head).
 template <typename TY>
 __global__ void __launch_bounds__(WARPS * 32)
-head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, const float* gate, int ld_gate, int gate_kind,
-                      TY* __restrict__ y, int items, int H, int dv, float eps) {
+head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, int w_per_head, const float* den, const float* gate,
+                      int ld_gate, int gate_kind, TY* __restrict__ y, int items, int H, int dv, float eps) {
     bl_pdl_trigger();
     bl_pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -449,15 +456,126 @@ head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, c
     if (item >= items) return;
     const int t = item / H, h = item % H;
     const float* src = o + (size_t)item * dv;
+    const float pre = den ? 1.0f / den[item] : 1.0f;
     float ss = 0.f;
-    for (int i = lane; i < dv; i += 32) ss += src[i] * src[i];
-    const float inv = 1.0f / sqrtf(bl_warp_sum(ss) / (float)dv + eps);
+    for (int i = lane; i < dv; i += 32) { const float u = src[i] * pre; ss += u * u; }
+    const float inv = pre / sqrtf(bl_warp_sum(ss) / (float)dv + eps);
     const float* g = gate ? gate + (size_t)t * ld_gate + h * dv : nullptr;
+    const size_t w0 = w_per_head ? (size_t)h * dv : 0;
     for (int i = lane; i < dv; i += 32) {
-        float val = src[i] * inv * bl_load_any(w, w_dtype, i);
+        float val = src[i] * inv * bl_load_any(w, w_dtype, w0 + i);
         if (g) val *= gate_kind == BL_GATE_SILU ? bl_silu(g[i]) : sigmoidf_(g[i]);
         bl_store(y + (size_t)item * dv + i, val);
     }
+}
+
+// The gates of a matrix memory with exponential gating, one warp per (request, head), the request's tokens in order.
+// Per token: log input gate i = cap tanh((zi + bi) / cap), log forget gate f = log sigmoid(cap tanh((zf + bf) / cap)), the
+// running maximum m' = max(f + m, i) (m starts at 0 in a fresh slot), decay a = e^(f + m - m'), input weight e = e^(i - m');
+// the normaliser n' = a n + e k per key channel, and den = max(|n' . q| q_scale, e^(-m')) + 1e-6. Out: the decay for every
+// key channel of the head (what the scan reads), e k, den. n [H, dk] and m [H] live in the slot at off_n and off_m.
+// Tokens are taken 32 at a time: the gates of 32 tokens in parallel (a lane each), the maxima as a chain of 32 steps of
+// two instructions, then the normaliser token by token with the lanes over the key channels.
+constexpr int GATE_MAX_ROWS = 16;                      // key channels a lane holds (dk <= 512)
+__global__ void __launch_bounds__(32)
+memory_gates_kernel(const float* proj, int ld, int off_q, int off_k, int off_i, int off_f, const void* __restrict__ bi, int bi_dtype,
+                    const void* __restrict__ bf, int bf_dtype, float cap, float q_scale, float* state, size_t slot_stride,
+                    size_t off_n, size_t off_m, const int* __restrict__ slots, const int* __restrict__ cu_q,
+                    float* a_out, float* k_out, float* den_out, int H, int dk) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int r = blockIdx.y, h = blockIdx.x, lane = threadIdx.x;
+    const int t0 = cu_q[r], n_tok = cu_q[r + 1] - t0;
+    if (n_tok <= 0) return;
+    float* slot = state + (size_t)slots[r] * slot_stride;
+    float* np = slot + off_n + (size_t)h * dk;
+    float nreg[GATE_MAX_ROWS];
+#pragma unroll
+    for (int j = 0; j < GATE_MAX_ROWS; ++j) nreg[j] = lane + 32 * j < dk ? np[lane + 32 * j] : 0.f;
+    float m = slot[off_m + h];
+    const float b_i = bl_load_any(bi, bi_dtype, h), b_f = bl_load_any(bf, bf_dtype, h);
+    const float inv_cap = 1.0f / cap;
+    for (int base = 0; base < n_tok; base += 32) {
+        const int cnt = min(32, n_tok - base);
+        float gi = 0.f, gf = 0.f;
+        if (lane < cnt) {
+            const float* row = proj + (size_t)(t0 + base + lane) * ld;
+            gi = cap * tanhf((row[off_i + h] + b_i) * inv_cap);
+            const float z = cap * tanhf((row[off_f + h] + b_f) * inv_cap);
+            gf = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+        }
+        float m_before = 0.f, m_mine = 0.f;
+        for (int tt = 0; tt < cnt; ++tt) {
+            const float f_t = __shfl_sync(0xffffffffu, gf, tt), i_t = __shfl_sync(0xffffffffu, gi, tt);
+            const float m_new = fmaxf(f_t + m, i_t);
+            if (lane == tt) { m_before = m; m_mine = m_new; }
+            m = m_new;
+        }
+        const float a_mine = expf(gf + m_before - m_mine), e_mine = expf(gi - m_mine), floor_mine = expf(-m_mine);
+        float den_mine = 0.f;
+        for (int tt = 0; tt < cnt; ++tt) {
+            const float a = __shfl_sync(0xffffffffu, a_mine, tt), e = __shfl_sync(0xffffffffu, e_mine, tt);
+            const size_t tok = (size_t)(t0 + base + tt);
+            const float* qr = proj + tok * ld + off_q + (size_t)h * dk;
+            const float* kr = proj + tok * ld + off_k + (size_t)h * dk;
+            float dot = 0.f;
+#pragma unroll
+            for (int j = 0; j < GATE_MAX_ROWS; ++j) {
+                const int c = lane + 32 * j;
+                if (c < dk) {
+                    const float ek = e * kr[c];
+                    nreg[j] = fmaf(a, nreg[j], ek);
+                    dot = fmaf(nreg[j], qr[c], dot);
+                    a_out[tok * H * dk + (size_t)h * dk + c] = a;
+                    k_out[tok * H * dk + (size_t)h * dk + c] = ek;
+                }
+            }
+            dot = bl_warp_sum(dot) * q_scale;
+            if (lane == tt) den_mine = fmaxf(fabsf(dot), floor_mine) + 1e-6f;
+        }
+        if (lane < cnt) den_out[(size_t)(t0 + base + lane) * H + h] = den_mine;
+    }
+#pragma unroll
+    for (int j = 0; j < GATE_MAX_ROWS; ++j) if (lane + 32 * j < dk) np[lane + 32 * j] = nreg[j];
+    if (lane == 0) slot[off_m + h] = m;
+}
+
+// Token shift: out[s, t, c] = x[t, c] + (x'[t, c] - x[t, c]) * mu[s, c] for s < n_mix, x' the row of the request's token
+// before (from the slot's `prev` [d] for a step's first token: zeros in a fresh slot). One block per token.
+template <typename TY>
+__global__ void __launch_bounds__(WARPS * 32)
+shift_mix_kernel(const float* x, int ld, const void* __restrict__ mu, int mu_dtype, int n_mix, const float* prev, size_t slot_stride,
+                 const int* __restrict__ slots, const int* __restrict__ tok_req, const int* __restrict__ cu_q, TY* __restrict__ out,
+                 int T, int d) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int t = blockIdx.x;
+    const int r = tok_req[t];
+    const float* before = t > cu_q[r] ? x + (size_t)(t - 1) * ld : prev + (size_t)slots[r] * slot_stride;
+    const float* cur = x + (size_t)t * ld;
+    for (int c = threadIdx.x; c < d; c += WARPS * 32) {
+        const float xc = cur[c], dx = before[c] - xc;
+        for (int s = 0; s < n_mix; ++s)
+            bl_store(out + ((size_t)s * T + t) * d + c, fmaf(dx, bl_load_any(mu, mu_dtype, (size_t)s * d + c), xc));
+    }
+}
+
+// b[t, h] = sum_c u[h, c] * k[t, h, c] * q[t, h, c]: what the current token adds to its own read-out; one warp per (t, h).
+__global__ void __launch_bounds__(WARPS * 32)
+bonus_dot_kernel(const float* q, int ldq, const float* k, int ldk, const void* __restrict__ u, int u_dtype, float* out,
+                 int items, int H, int dk) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int t = item / H, h = item % H;
+    const float* qr = q + (size_t)t * ldq + (size_t)h * dk;
+    const float* kr = k + (size_t)t * ldk + (size_t)h * dk;
+    float acc = 0.f;
+    for (int c = lane; c < dk; c += 32) acc = fmaf(bl_load_any(u, u_dtype, (size_t)h * dk + c) * kr[c], qr[c], acc);
+    acc = bl_warp_sum(acc);
+    if (lane == 0) out[item] = acc;
 }
 
 // One block per token: y[t, ch] = silu(sum_i taps[ch, i] * x[t - (n_taps - 1) + i, ch]), the inputs before the step's
@@ -530,7 +648,7 @@ extern "C" int bl_recurrent_scan(int rule, const float* q, int ldq, const float*
 // 0, or the blocks that each part of one request's portion runs on in the first pass, H * ceil(columns / columns a
 // block) (the delta rule's first pass has dk columns more, and its fold takes key sizes up to 128).
 extern "C" int bl_recurrent_scan_can_split(int rule, int H, int dk, int dv) {
-    if (rule != BL_RULE_GLA && rule != BL_RULE_DELTA) return 0;
+    if (rule != BL_RULE_GLA && rule != BL_RULE_DELTA && rule != BL_RULE_BONUS) return 0;
     if (rule == BL_RULE_DELTA && dk > FOLD_MAX_DK) return 0;
     for (int ks = 1; ks <= 32; ks *= 2)
         if (dk % (4 * ks) == 0 && dk / ks <= SCAN_VEC_ROWS) {
@@ -556,7 +674,7 @@ extern "C" int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const 
     if (H <= 0 || G <= 0 || H % G != 0 || dk <= 0 || dv <= 0) BL_FAIL("bl_recurrent_scan: bad sizes H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
     if (dk > RKMAX * 32) BL_FAIL("bl_recurrent_scan: %d key channels, at most %d", dk, RKMAX * 32);
     if (R > 65535 || H > 65535) BL_FAIL("bl_recurrent_scan: %d requests or %d heads are too many for one launch", R, H);
-    if (rule == BL_RULE_DELTA && beta == nullptr) BL_FAIL("bl_recurrent_scan: the delta rule needs beta");
+    if ((rule == BL_RULE_DELTA || rule == BL_RULE_BONUS) && beta == nullptr) BL_FAIL("bl_recurrent_scan: rule %d needs beta", rule);
     int KS = 1;
     while ((dk + KS - 1) / KS > RKMAX) KS *= 2;
     // The kernel with 16-byte fetches where the key size splits evenly over the lanes. Sixteen rows a lane: eight, with a
@@ -579,13 +697,13 @@ extern "C" int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const 
     dim3 grid((dv + cols_blk - 1) / cols_blk, H, R * nc);
     const dim3 grid_wide((dv + dk + cols_blk - 1) / cols_blk, H, R * nc);     // the delta rule's first pass
     cudaStream_t s = (cudaStream_t)stream;
-    if (rule != BL_RULE_GLA && rule != BL_RULE_DELTA) BL_FAIL("bl_recurrent_scan: unknown rule %d", rule);
+    if (rule != BL_RULE_GLA && rule != BL_RULE_DELTA && rule != BL_RULE_BONUS) BL_FAIL("bl_recurrent_scan: unknown rule %d", rule);
     if (rk4 > 0) {                                     // a lane's rows are whole groups of four
         const bool dl = rule == BL_RULE_DELTA;
         float* part_s = scratch;                                                 // [R, nc, H, dk, dv]
         float* part_p = scratch ? scratch + (size_t)R * nc * H * dk * dv : nullptr;   // [R, nc, H, dk] or, delta rule, [R, nc, H, dk, dk]
         float* part_start = (scratch && dl) ? part_p + (size_t)R * nc * H * dk * dk : nullptr;   // delta rule: [R, nc, H, dk, dv]
-#define BL_SCAN(D, R4, PASS) BL_CUDA(bl_launch_dependent(recurrent_scan_vec_kernel<D, R4>, (D && PASS == 1) ? grid_wide : grid, dim3(WARPS * 32), smem, s, \
+#define BL_SCAN(D, R4, PASS) BL_CUDA(bl_launch_dependent(recurrent_scan_vec_kernel<D, R4>, (D == BL_RULE_DELTA && PASS == 1) ? grid_wide : grid, dim3(WARPS * 32), smem, s, \
         q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale, state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec, nc, PASS, \
         part_s, part_p, (const float*)part_start))
         for (int pass = (nc > 1 ? 1 : 2); pass <= 2; ++pass) {
@@ -594,10 +712,13 @@ extern "C" int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const 
                                             (size_t)slot_stride, slots, cu_q, (const float*)part_s, (const float*)part_p, part_start,
                                             H, dk, dv, nc));
             switch (rk4) {
-                case 1: if (dl) BL_SCAN(true, 1, pass); else BL_SCAN(false, 1, pass); break;
-                case 2: if (dl) BL_SCAN(true, 2, pass); else BL_SCAN(false, 2, pass); break;
-                case 3: if (dl) BL_SCAN(true, 3, pass); else BL_SCAN(false, 3, pass); break;
-                default: if (dl) BL_SCAN(true, 4, pass); else BL_SCAN(false, 4, pass); break;
+#define BL_SCAN_RULE(R4) do { if (dl) BL_SCAN(BL_RULE_DELTA, R4, pass); else if (rule == BL_RULE_BONUS) BL_SCAN(BL_RULE_BONUS, R4, pass); \
+                                  else BL_SCAN(BL_RULE_GLA, R4, pass); } while (0)
+                case 1: BL_SCAN_RULE(1); break;
+                case 2: BL_SCAN_RULE(2); break;
+                case 3: BL_SCAN_RULE(3); break;
+                default: BL_SCAN_RULE(4); break;
+#undef BL_SCAN_RULE
             }
         }
 #undef BL_SCAN
@@ -609,32 +730,82 @@ extern "C" int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const 
     }
     if (nc > 1) BL_FAIL("bl_recurrent_scan_parts: %d key channels cannot be cut into parts", dk);
     if (rule == BL_RULE_GLA)
-        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<false>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale,
+        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<BL_RULE_GLA>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale,
             state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec));
     else if (rule == BL_RULE_DELTA)
-        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<true>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale,
+        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<BL_RULE_DELTA>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale,
             state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec));
     else
-        BL_FAIL("bl_recurrent_scan: unknown rule %d", rule);
+        BL_CUDA(bl_launch_dependent(recurrent_scan_kernel<BL_RULE_BONUS>, grid, dim3(WARPS * 32), smem, s, q, ldq, k, ldk, v, ldv, z, ldz, beta, ldb, q_scale,
+            state, (size_t)slot_stride, slots, cu_q, out, H, G, dk, dv, KS, chunk, vec));
     BL_CHECK_LAUNCH("bl_recurrent_scan");
     return 0;
 }
 
 extern "C" int bl_head_norm_gate(const float* o, const void* w, int w_dtype, const float* gate, int ld_gate, int gate_kind,
                                  void* y, int y_dtype, int T, int H, int dv, float eps, void* stream) {
+    return bl_head_norm_gate_ext(o, w, w_dtype, 0, nullptr, gate, ld_gate, gate_kind, y, y_dtype, T, H, dv, eps, stream);
+}
+
+extern "C" int bl_head_norm_gate_ext(const float* o, const void* w, int w_dtype, int w_per_head, const float* den, const float* gate,
+                                     int ld_gate, int gate_kind, void* y, int y_dtype, int T, int H, int dv, float eps, void* stream) {
     if (T <= 0) return 0;
     if (H <= 0 || dv <= 0 || (gate && ld_gate < H * dv)) BL_FAIL("bl_head_norm_gate: bad sizes H=%d dv=%d gate stride %d", H, dv, ld_gate);
     if (gate && gate_kind != BL_GATE_SIGMOID && gate_kind != BL_GATE_SILU) BL_FAIL("bl_head_norm_gate: unknown gate %d", gate_kind);
     const int items = T * H, blocks = (items + WARPS - 1) / WARPS;
     cudaStream_t s = (cudaStream_t)stream;
     if (y_dtype == BL_F32)
-        BL_CUDA(bl_launch_dependent(head_norm_gate_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, s, o, w, w_dtype, gate, ld_gate, gate_kind, (float*)y, items, H, dv, eps));
+        BL_CUDA(bl_launch_dependent(head_norm_gate_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, s, o, w, w_dtype, w_per_head, den, gate,
+                                    ld_gate, gate_kind, (float*)y, items, H, dv, eps));
     else if (y_dtype == BL_BF16)
-        BL_CUDA(bl_launch_dependent(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, s, o, w, w_dtype, gate,
-                                    ld_gate, gate_kind, (__nv_bfloat16*)y, items, H, dv, eps));
+        BL_CUDA(bl_launch_dependent(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, s, o, w, w_dtype, w_per_head, den,
+                                    gate, ld_gate, gate_kind, (__nv_bfloat16*)y, items, H, dv, eps));
     else
         BL_FAIL("bl_head_norm_gate: unknown output dtype %d", y_dtype);
     BL_CHECK_LAUNCH("bl_head_norm_gate");
+    return 0;
+}
+
+extern "C" int bl_memory_gates(const float* proj, int ld, int off_q, int off_k, int off_i, int off_f, const void* bias_i, int bi_dtype,
+                               const void* bias_f, int bf_dtype, float cap, float q_scale, float* state, long long slot_stride,
+                               long long off_n, long long off_m, const int* slots, const int* cu_q, int R, float* a_out, float* k_out,
+                               float* den_out, int H, int dk, void* stream) {
+    if (R <= 0) return 0;
+    if (H <= 0 || dk <= 0 || dk > GATE_MAX_ROWS * 32 || !(cap > 0.f)) BL_FAIL("bl_memory_gates: bad sizes H=%d dk=%d cap=%g", H, dk, cap);
+    if (R > 65535) BL_FAIL("bl_memory_gates: %d requests are too many for one launch", R);
+    if (off_q + H * dk > ld || off_k + H * dk > ld || off_i + H > ld || off_f + H > ld) BL_FAIL("bl_memory_gates: columns do not fit rows of %d", ld);
+    BL_CUDA(bl_launch_dependent(memory_gates_kernel, dim3(H, R), dim3(32), 0, (cudaStream_t)stream, proj, ld, off_q, off_k, off_i, off_f,
+                                bias_i, bi_dtype, bias_f, bf_dtype, cap, q_scale, state, (size_t)slot_stride, (size_t)off_n, (size_t)off_m,
+                                slots, cu_q, a_out, k_out, den_out, H, dk));
+    BL_CHECK_LAUNCH("bl_memory_gates");
+    return 0;
+}
+
+extern "C" int bl_shift_mix(const float* x, int ld, const void* mu, int mu_dtype, int n_mix, const float* prev, long long slot_stride,
+                            const int* slots, const int* tok_req, const int* cu_q, void* out, int out_dtype, int T, int d, void* stream) {
+    if (T <= 0) return 0;
+    if (d <= 0 || ld < d || n_mix < 1) BL_FAIL("bl_shift_mix: bad sizes d=%d ld=%d mixes=%d", d, ld, n_mix);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == BL_F32)
+        BL_CUDA(bl_launch_dependent(shift_mix_kernel<float>, dim3(T), dim3(WARPS * 32), 0, s, x, ld, mu, mu_dtype, n_mix, prev,
+                                    (size_t)slot_stride, slots, tok_req, cu_q, (float*)out, T, d));
+    else if (out_dtype == BL_BF16)
+        BL_CUDA(bl_launch_dependent(shift_mix_kernel<__nv_bfloat16>, dim3(T), dim3(WARPS * 32), 0, s, x, ld, mu, mu_dtype, n_mix, prev,
+                                    (size_t)slot_stride, slots, tok_req, cu_q, (__nv_bfloat16*)out, T, d));
+    else
+        BL_FAIL("bl_shift_mix: unknown output dtype %d", out_dtype);
+    BL_CHECK_LAUNCH("bl_shift_mix");
+    return 0;
+}
+
+extern "C" int bl_bonus_dot(const float* q, int ldq, const float* k, int ldk, const void* u, int u_dtype, float* out, int T, int H,
+                            int dk, void* stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || dk <= 0 || ldq < H * dk || ldk < H * dk) BL_FAIL("bl_bonus_dot: bad sizes H=%d dk=%d", H, dk);
+    const int items = T * H;
+    BL_CUDA(bl_launch_dependent(bonus_dot_kernel, dim3((items + WARPS - 1) / WARPS), dim3(WARPS * 32), 0, (cudaStream_t)stream, q, ldq, k, ldk,
+                                u, u_dtype, out, items, H, dk));
+    BL_CHECK_LAUNCH("bl_bonus_dot");
     return 0;
 }
 

@@ -789,7 +789,7 @@ def norm_qkv_rope(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w_qkv: torc
 # ---- norms with bias, gated residuals, the average over the layers' streams ----------------------------------------
 ACT_SILU, ACT_GELU_ERF, ACT_GELU_TANH = 0, 1, 2
 GATE_SIGMOID, GATE_SILU = 0, 1
-RULE_GLA, RULE_DELTA = 0, 1
+RULE_GLA, RULE_DELTA, RULE_BONUS = 0, 1, 2
 
 
 def _rows32(t: torch.Tensor, name: str, rows: int, min_cols: int) -> int:
@@ -918,7 +918,8 @@ def recurrent_scan_parts(rule: int, H: int, dk: int, dv: int, n_long: int) -> in
 def recurrent_scan(rule: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: Optional[torch.Tensor],
                    q_scale: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, out: torch.Tensor,
                    H: int, G: int, dk: int, dv: int, parts: int = 1) -> None:
-    """A linear recurrence over a matrix state per head and request (`RULE_GLA`, `RULE_DELTA`; see `bl_recurrent_scan`).
+    """A linear recurrence over a matrix state per head and request (`RULE_GLA`, `RULE_DELTA`, `RULE_BONUS`, whose beta is
+    a given number per token and head, see `bonus_dot`; see `bl_recurrent_scan`).
     q, k [T, G * dk], v [T, H * dv], decay [T, H * dk] (in (0, 1], see `gemm_plain_decay`), beta [T, H] (logits): 32-bit
     rows, possibly column ranges of a wider matrix. state: [slots, >= H * dk * dv] 32-bit, the matrix state first in each
     slot. out [T, H * dv] 32-bit, already times q_scale. `parts` > 1 (`recurrent_scan_parts`): portions of 256 tokens and
@@ -1040,3 +1041,197 @@ def norm_chain(x: torch.Tensor, sub: Optional[torch.Tensor] = None, gate: Option
     _call(_lib().bl_norm_chain, _p(x), _p(sub), _p(gate), ld, _p(gate_bias), dt(gate_bias), _p(pw), dt(pw), _p(pb), dt(pb),
           ctypes.c_float(peps), _p(streams), ctypes.c_longlong(stride), _p(coeffs), dt(coeffs), n, _p(mix_out), _p(tw), dt(tw),
           _p(tb), dt(tb), ctypes.c_float(teps), _p(y), dt(y) if y is not None else 0, rows, d, _stream())
+
+
+# ---- layers with the norm behind the sublayer; mixers and feed-forwards of newer designs -----------------------------
+
+def _vec_dt(t: Optional[torch.Tensor]) -> int:
+    return _dt(t) if t is not None else 0
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (32-bit, contiguous) in out's dtype."""
+    _need(x, "x", torch.float32); _need(out, "out", None, tuple(x.shape))
+    _call(_lib().bl_cast_rows, _p(x), _p(out), _dt(out), ctypes.c_longlong(x.numel()), _stream())
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x = cap * tanh(x / cap), in place (32-bit)."""
+    _need(x, "x", torch.float32)
+    _call(_lib().bl_softcap, _p(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), _stream())
+
+
+def post_norm_residual(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float, y: Optional[torch.Tensor] = None,
+                       b: Optional[torch.Tensor] = None, wa: Optional[torch.Tensor] = None, wb: Optional[torch.Tensor] = None,
+                       rms_eps: float = 0.0) -> None:
+    """x += LN(s) * weight (layer norm without bias) with s = a, or, with b, s = (rms_norm(a) * wa + rms_norm(b) * wb) / 2;
+    y (optional): the new rows of x in y's dtype as well (what the next sublayer's products read)."""
+    rows, d = x.shape
+    _need(x, "x", torch.float32); _need(a, "a", torch.float32, (rows, d)); _need(weight, "weight", None, (d,))
+    if b is not None:
+        _need(b, "b", torch.float32, (rows, d)); _need(wa, "wa", None, (d,)); _need(wb, "wb", None, (d,))
+    if y is not None:
+        _need(y, "y", None, (rows, d))
+    _call(_lib().bl_post_norm_residual, _p(x), _p(a), _p(wa), _vec_dt(wa), _p(b), _p(wb), _vec_dt(wb), ctypes.c_float(rms_eps),
+          _p(weight), _dt(weight), ctypes.c_float(eps), _p(y), _dt(y) if y is not None else 0, rows, d, _stream())
+
+
+def pair_rms_mean(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, rms_eps: float, out: torch.Tensor) -> None:
+    """out = (rms_norm(a) * wa + rms_norm(b) * wb) / 2, row by row, 32-bit."""
+    rows, d = a.shape
+    _need(a, "a", torch.float32); _need(b, "b", torch.float32, (rows, d)); _need(out, "out", torch.float32, (rows, d))
+    _need(wa, "wa", None, (d,)); _need(wb, "wb", None, (d,))
+    _call(_lib().bl_pair_rms_mean, _p(a), _p(wa), _dt(wa), _p(b), _p(wb), _dt(wb), ctypes.c_float(rms_eps), _p(out), rows, d, _stream())
+
+
+def qk_head_norm_rope_write(proj: torch.Tensor, off_k: int, off_v: int, q_norm_w: Optional[torch.Tensor],
+                            k_norm_w: Optional[torch.Tensor], eps: float, positions: torch.Tensor, tok_req: torch.Tensor,
+                            block_table: torch.Tensor, inv_freq: torch.Tensor, rot_half: int, pair_layout: int, q_out: torch.Tensor,
+                            k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], H: int, KV: int, dk: int, dv: int) -> None:
+    """`qk_norm_rope_write` with an RMS norm over each HEAD of q and of k (weights [dk], shared by the heads)."""
+    T = proj.shape[0]
+    ld = _rows32(proj, "proj", T, off_v + KV * dv)
+    _need(positions, "positions", torch.int32, (T,)); _need(tok_req, "tok_req", torch.int32, (T,))
+    _need(block_table, "block_table", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
+    if inv_freq.numel() < rot_half:
+        raise KernelError("inv_freq: fewer entries than rotated pairs")
+    _need(q_out, "q_out", None, (T, H * dk))
+    for w, name in ((q_norm_w, "q_norm_w"), (k_norm_w, "k_norm_w")):
+        if w is not None:
+            _need(w, name, None, (dk,))
+    page_size = 1
+    if k_cache is not None:
+        _need(k_cache, "k_cache", q_out.dtype); _need(v_cache, "v_cache", q_out.dtype)
+        if tuple(k_cache.shape[1:]) != (KV, k_cache.shape[2], dk) or tuple(v_cache.shape) != (k_cache.shape[0], KV, k_cache.shape[2], dv):
+            raise KernelError(f"caches {tuple(k_cache.shape)} / {tuple(v_cache.shape)} do not hold {KV} heads of {dk} / {dv}")
+        page_size = k_cache.shape[2]
+    _call(_lib().bl_qk_norm_rope_write_scope, _p(proj), ld, off_k, off_v, _p(q_norm_w), _vec_dt(q_norm_w), _p(k_norm_w),
+          _vec_dt(k_norm_w), ctypes.c_float(eps), 1, _p(positions), _p(tok_req), _p(block_table), block_table.shape[1],
+          _p(inv_freq), rot_half, pair_layout, _p(q_out), _p(k_cache), _p(v_cache), _dt(q_out), T, H, KV, dk, dv, page_size, _stream())
+
+
+def attention_talk_plain(q, k_cache, v_cache, tok_req, cu_q, ctx_len, block_table, A: torch.Tensor, H: int, chunk: int, window: int,
+                         scale: float, head_scale: Optional[torch.Tensor]) -> None:
+    """A[t, g, c] = sum_j softmax_j(q_g . k_kv(g)(j) * scale * head_scale[g]) v_c(j) over the keys of the query's chunk
+    (positions [i - i % chunk, i]; chunk 0: all before it; window > 0: also the last `window` only): every head's softmax
+    applied to the values of every key/value head. A: 32-bit [T, H, KV, dv]."""
+    T = q.shape[0]
+    KV, page_size, dh = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    dv = v_cache.shape[3]
+    _need(q, "q", None, (T, H * dh)); _need(k_cache, "k_cache", q.dtype); _need(v_cache, "v_cache", q.dtype)
+    _need(A, "A", torch.float32, (T, H, KV, dv)); _need(block_table, "block_table", torch.int32)
+    if head_scale is not None:
+        _need(head_scale, "head_scale", None, (H,))
+    _call(_lib().bl_attention_talk_plain, _p(q), _p(k_cache), _p(v_cache), _dt(q), _p(tok_req), _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(A), T, H, KV, dh, dv, page_size, chunk, window, ctypes.c_float(scale), _p(head_scale),
+          _vec_dt(head_scale), _stream())
+
+
+def talk_mix(A: torch.Tensor, talk: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, h] = sum_g talk[h, g] * A[t, g, kv(h)]: the heads' softmax weights mixed, applied to each head's own values."""
+    T, H, KV, dv = A.shape
+    _need(A, "A", torch.float32); _need(talk, "talk", None, (H, H)); _need(out, "out", None, (T, H * dv))
+    _call(_lib().bl_talk_mix, _p(A), _p(talk), _dt(talk), _p(out), _dt(out), T, H, KV, dv, _stream())
+
+
+def gemm_plain_decay_exp(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, x_tanh: bool = False) -> None:
+    """out[m, n] = exp(-exp(u[m] . w[n] + bias[n])), u = tanh(x) with `x_tanh`, 32-bit: decays in (0, 1) from a product in
+    two factors (x: the first factor's 32-bit sums, possibly a column range of a wider matrix)."""
+    M, K = x.shape
+    N = out.shape[1]
+    ld = _rows32(x, "x", M, K)
+    _need(w, "w", None, (N, K)); _need(out, "out", torch.float32, (M, N))
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    _call(_lib().bl_gemm_plain_decay_exp, _p(x), ld, 1 if x_tanh else 0, _p(w), _dt(w), _p(bias), _vec_dt(bias), _p(out), M, N, K, _stream())
+
+
+def _slot_rows(state: torch.Tensor, name: str, min_cols: int) -> None:
+    if not state.is_cuda or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < min_cols:
+        raise KernelError(f"{name}: must be 32-bit [slots, >= {min_cols}] with contiguous rows")
+
+
+def memory_gates(proj: torch.Tensor, off_q: int, off_k: int, off_i: int, off_f: int, bias_i: torch.Tensor, bias_f: torch.Tensor,
+                 cap: float, q_scale: float, state: torch.Tensor, off_n: int, off_m: int, slots: torch.Tensor, cu_q: torch.Tensor,
+                 decay: torch.Tensor, k_out: torch.Tensor, den: torch.Tensor, H: int, dk: int) -> None:
+    """The gates of a matrix memory with exponential gating held against a running maximum (see `bl_memory_gates`): from
+    the joined projections, per token and head, the decay (written for every key channel: what `recurrent_scan` reads),
+    the keys times their input weight, and the read-out's denominator; the normaliser [H, dk] and the maximum [H] are kept
+    in the request's slot at `off_n` and `off_m`."""
+    T = proj.shape[0]
+    ld = _rows32(proj, "proj", T, 1)
+    _slot_rows(state, "state", max(off_n + H * dk, off_m + H))
+    _need(decay, "decay", torch.float32, (T, H * dk)); _need(k_out, "k_out", torch.float32, (T, H * dk)); _need(den, "den", torch.float32, (T, H))
+    _need(bias_i, "bias_i", None, (H,)); _need(bias_f, "bias_f", None, (H,))
+    _need(slots, "slots", torch.int32); _need(cu_q, "cu_q", torch.int32)
+    _call(_lib().bl_memory_gates, _p(proj), ld, off_q, off_k, off_i, off_f, _p(bias_i), _dt(bias_i), _p(bias_f), _dt(bias_f),
+          ctypes.c_float(cap), ctypes.c_float(q_scale), _p(state), ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(off_n),
+          ctypes.c_longlong(off_m), _p(slots), _p(cu_q), cu_q.shape[0] - 1, _p(decay), _p(k_out), _p(den), H, dk, _stream())
+
+
+def head_norm_gate_ext(o: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], gate_kind: int, eps: float,
+                       out: torch.Tensor, H: int, dv: int, den: Optional[torch.Tensor] = None) -> None:
+    """`head_norm_gate` with a weight per head and channel when `weight` has H * dv values, and an optional divisor
+    den [T, H] applied to o before the norm."""
+    T = o.shape[0]
+    _need(o, "o", torch.float32, (T, H * dv)); _need(out, "out", None, (T, H * dv))
+    per_head = weight.numel() == H * dv and H > 1
+    _need(weight, "weight", None, (H * dv,) if per_head else (dv,))
+    if den is not None:
+        _need(den, "den", torch.float32, (T, H))
+    ld = _rows32(gate, "gate", T, H * dv) if gate is not None else 0
+    _call(_lib().bl_head_norm_gate_ext, _p(o), _p(weight), _dt(weight), 1 if per_head else 0, _p(den), _p(gate), ld, gate_kind,
+          _p(out), _dt(out), T, H, dv, ctypes.c_float(eps), _stream())
+
+
+def shift_mix(x: torch.Tensor, mu: torch.Tensor, prev: torch.Tensor, slots: torch.Tensor, tok_req: torch.Tensor, cu_q: torch.Tensor,
+              out: torch.Tensor) -> None:
+    """out[s, t] = x[t] + (x[t - 1] - x[t]) * mu[s] within each request; the row before a step's first token of a request is
+    its slot's `prev` [slots, >= d] (keep it with `conv_tail_update(x, 2, prev, ...)` after this call)."""
+    T, d = x.shape
+    n_mix = mu.shape[0]
+    ld = _rows32(x, "x", T, d)
+    _need(mu, "mu", None, (n_mix, d)); _need(out, "out", None, (n_mix, T, d)); _slot_rows(prev, "prev", d)
+    _need(slots, "slots", torch.int32); _need(tok_req, "tok_req", torch.int32, (T,)); _need(cu_q, "cu_q", torch.int32)
+    _call(_lib().bl_shift_mix, _p(x), ld, _p(mu), _dt(mu), n_mix, _p(prev), ctypes.c_longlong(prev.stride(0)), _p(slots), _p(tok_req),
+          _p(cu_q), _p(out), _dt(out), T, d, _stream())
+
+
+def bonus_dot(q: torch.Tensor, k: torch.Tensor, u: torch.Tensor, out: torch.Tensor, H: int, dk: int) -> None:
+    """out[t, h] = sum_c u[h, c] * k[t, h, c] * q[t, h, c]: the beta of `RULE_BONUS` for a bonus per head and key channel."""
+    T = out.shape[0]
+    ldq, ldk = _rows32(q, "q", T, H * dk), _rows32(k, "k", T, H * dk)
+    _need(u, "u", None, (H, dk)); _need(out, "out", torch.float32, (T, H))
+    _call(_lib().bl_bonus_dot, _p(q), ldq, _p(k), ldk, _p(u), _dt(u), _p(out), T, H, dk, _stream())
+
+
+def moe_route(z: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_groups: int, keep: int, ids: torch.Tensor,
+              wts: torch.Tensor) -> None:
+    """The experts of each token and their weights from the router's 32-bit logits z [T, E] (see `bl_moe_route`)."""
+    T, E = z.shape
+    ld = _rows32(z, "z", T, E)
+    if correction is not None:
+        _need(correction, "correction", None, (E,))
+    _need(ids, "ids", torch.int32, (T, top)); _need(wts, "wts", torch.float32, (T, top))
+    _call(_lib().bl_moe_route, _p(z), ld, _p(correction), _vec_dt(correction), T, E, top, n_groups, keep, _p(ids), _p(wts), _stream())
+
+
+def expert_gemm_plain(x: torch.Tensor, x_div: int, w: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE) -> None:
+    """out[p] = epilogue(x[p // x_div] @ w[ids[p]].T): rows that each use the matrix of their own expert. w [E, N, K]
+    ([E, 2N, K], gate rows then up rows, for EPI_SWIGLU)."""
+    P, N = out.shape
+    K = x.shape[1]
+    _need(x, "x"); _need(w, "w", x.dtype); _need(out, "out"); _need(ids, "ids", torch.int32)
+    rows_w = 2 * N if epilogue == EPI_SWIGLU else N
+    if w.dim() != 3 or w.shape[1] != rows_w or w.shape[2] != K or ids.numel() != P or x.shape[0] * x_div != P:
+        raise KernelError(f"expert_gemm_plain: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, {ids.numel()} ids do not fit")
+    _call(_lib().bl_expert_gemm_plain, _p(x), _dt(x), x_div, _p(w), _dt(w), ctypes.c_longlong(w.stride(0)), _p(ids), _p(out), _dt(out),
+          P, N, K, epilogue, _stream())
+
+
+def moe_combine(y: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, add: bool = False) -> None:
+    """out[t] = sum_k wts[t, k] * y[t * top + k], k ascending (32-bit); with `add` the sum is added to out."""
+    T, top = wts.shape
+    d = out.shape[1]
+    _need(y, "y", torch.float32, (T * top, d)); _need(wts, "wts", torch.float32); _need(out, "out", torch.float32, (T, d))
+    _call(_lib().bl_moe_combine, _p(y), _p(wts), _p(out), T, top, d, 1 if add else 0, _stream())

@@ -1,5 +1,5 @@
 """Architectures of this engine. Importing the package registers them."""
-from . import qwen2, fezopel
+from . import qwen2, fezopel, kavotar
 from .loading import build_model, load_model, load_random_model, write_random_model
 
-__all__ = ["qwen2", "fezopel", "build_model", "load_model", "load_random_model", "write_random_model"]
+__all__ = ["qwen2", "fezopel", "kavotar", "build_model", "load_model", "load_random_model", "write_random_model"]

@@ -2,10 +2,10 @@ from .base import Part, StepContext, StepPlan, to_device_matrix, to_device_vecto
 from .linear import linear
 from .norm import RMSNorm, LayerNorm
 from .rotary import RotaryTable
-from .attention import Mixer, GQAAttention, GatedSinkAttention
-from .recurrent import GatedLinearAttention, ChannelDeltaRule
-from .feedforward import FeedForward, SwiGLU, DenseMLP
-from .block import PreNormBlock, GatedSandwichBlock, ResidualGate
+from .attention import Mixer, GQAAttention, GatedSinkAttention, ChunkedTalkingAttention, ParallelMixers
+from .recurrent import GatedLinearAttention, ChannelDeltaRule, MatrixMemory, ShiftedDecayRecurrence
+from .feedforward import FeedForward, SwiGLU, DenseMLP, RoutedExperts
+from .block import PreNormBlock, GatedSandwichBlock, ResidualGate, PostNormBlock
 from .depth import DepthWeightedAverage
 from .embedding import Embedding, OutputHead
 from .model import DecoderModel, LayerCall
@@ -13,5 +13,6 @@ from .model import DecoderModel, LayerCall
 __all__ = ["Part", "StepContext", "StepPlan", "to_device_matrix", "to_device_vector", "linear", "RMSNorm",
            "LayerNorm", "RotaryTable", "Mixer", "GQAAttention", "GatedSinkAttention", "GatedLinearAttention",
            "ChannelDeltaRule", "FeedForward", "SwiGLU", "DenseMLP", "PreNormBlock", "GatedSandwichBlock", "ResidualGate",
+           "ChunkedTalkingAttention", "ParallelMixers", "MatrixMemory", "ShiftedDecayRecurrence", "RoutedExperts", "PostNormBlock",
            "DepthWeightedAverage",
            "Embedding", "OutputHead", "DecoderModel", "LayerCall"]

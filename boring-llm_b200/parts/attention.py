@@ -361,3 +361,121 @@ class GatedSinkAttention(Mixer):
 
     def attend(self, ctx, q, k_cache, v_cache, table, out, gate):
         paged_attention(ctx, q, k_cache, v_cache, table, out, self.H, self.KV, self.dk, self.window, self.scale, self.sinks, gate)
+
+
+class ChunkedTalkingAttention(Mixer):
+    """Grouped-query attention over the query's own chunk of positions, with the heads' softmax weights mixed afterwards:
+
+    * q and k get an RMS norm per head (`qk_norm_eps`; weights of the head size, shared by the heads) before the rotation;
+    * `rotary`: any `RotaryTable` (partial rotation, pairs in halves or interleaved);
+    * score = q . k * scale * temp[head], `temp` a learned number per head;
+    * `chunk` n > 0: position i sees j <= i with floor(i / n) = floor(j / n), chunks counted from position 0 of the
+      sequence (0: every j <= i); `window` as in `GQAAttention`, on top of it;
+    * softmax per head over the visible keys; then W'_h = sum_g talk[h, g] W_g (`talk` [H, H]), and head h applies W'_h to
+      the values of its own key/value head; values may have another head size than keys.
+
+    The mix is linear, so the kernels apply every head's softmax to the values of every key/value head in one pass over
+    the keys and mix the results (`ops.attention_talk_plain`, `ops.talk_mix`); the cache manager gives back the pages that
+    lie before the chunk of the next position."""
+    graph_safe = True
+
+    def __init__(self, dim: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: Optional[int],
+                 rotary: Optional[RotaryTable], names: Dict[str, str], chunk: int = 0, window: int = 0,
+                 scale: Optional[float] = None, qk_norm_eps: float = 1e-6):
+        super().__init__(names)
+        if n_heads % n_kv_heads != 0:
+            raise ValueError(f"{n_heads} query heads cannot share {n_kv_heads} key/value heads")
+        self.dim, self.H, self.KV, self.dk = dim, n_heads, n_kv_heads, head_dim
+        self.dv = head_dim if v_head_dim is None else int(v_head_dim)
+        self.rotary = rotary if rotary is not None else RotaryTable(head_dim, 10000.0, n_rot=0)
+        self.chunk, self.window = int(chunk), int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.qk_norm_eps = float(qk_norm_eps)
+        self.off_k = self.H * self.dk
+        self.off_v = self.off_k + self.KV * self.dk
+        self.w_in = self.wo = self.q_norm = self.k_norm = self.talk = self.temp = None
+
+    def local_specs(self):
+        return {"wq": TensorSpec((self.H * self.dk, self.dim), MATRIX), "wk": TensorSpec((self.KV * self.dk, self.dim), MATRIX),
+                "wv": TensorSpec((self.KV * self.dv, self.dim), MATRIX), "wo": TensorSpec((self.dim, self.H * self.dv), MATRIX),
+                "q_norm": TensorSpec((self.dk,), NORM), "k_norm": TensorSpec((self.dk,), NORM),
+                "talk": TensorSpec((self.H, self.H), MATRIX), "temp": TensorSpec((self.H,), BIAS)}
+
+    def place(self, local, dtype, device):
+        self.w_in = to_device_matrix(torch.cat([local["wq"], local["wk"], local["wv"]], dim=0), dtype, device)
+        self.wo = to_device_matrix(local["wo"], dtype, device)
+        self.q_norm = to_device_vector(local["q_norm"], dtype, device)
+        self.k_norm = to_device_vector(local["k_norm"], dtype, device)
+        self.talk = local["talk"].to(device=device, dtype=torch.float32).contiguous()
+        self.temp = local["temp"].to(device=device, dtype=torch.float32).contiguous()
+        self.rotary.to(device)
+
+    def cache_spec(self):
+        return PagedKVSpec(self.KV, self.dk, self.window, 0 if self.dv == self.dk else self.dv, self.chunk)
+
+    def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
+        T = h.shape[0]
+        k_cache, v_cache, table = ctx.kv(cache_layer)
+        proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
+        linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        self._joined(proj)
+        q = ctx.empty((T, self.H * self.dk))
+        ops.qk_head_norm_rope_write(proj, self.off_k, self.off_v, self.q_norm, self.k_norm, self.qk_norm_eps, ctx.positions,
+                                    ctx.tok_req, table, self.rotary.inv_freq, self.rotary.rot_half, self.rotary.pair_layout, q,
+                                    k_cache if write_cache else None, v_cache if write_cache else None, self.H, self.KV,
+                                    self.dk, self.dv)
+        spread = ctx.empty((T, self.H, self.KV, self.dv), torch.float32)
+        ops.attention_talk_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, spread, self.H, self.chunk,
+                                 self.window, self.scale, self.temp)
+        attn = ctx.empty((T, self.H * self.dv))
+        ops.talk_mix(spread, self.talk, attn)
+        linear(ctx, attn, self.wo, out, None, epilogue)
+
+    def forward(self, ctx, h, residual, cache_layer, write_cache=True):
+        self._run(ctx, h, residual, cache_layer, write_cache, EPI_RESIDUAL)
+
+    def mix(self, ctx, h, out, cache_layer, write_cache=True):
+        self._run(ctx, h, out, cache_layer, write_cache, EPI_NONE)
+
+
+class ParallelMixers(Mixer):
+    """Two mixers side by side that read the same rows; the result is the mean of the two, each RMS-normed over the
+    model width first with a plain weight of its own: (rms_norm(left(h)) * left_out + rms_norm(right(h)) * right_out) / 2.
+    Each mixer keeps its own cache, so this part's `cache_spec()` is the pair of theirs and it is handed a pair of cache
+    layers. A block that adds the result to the stream through a norm can take the two results as they are
+    (`mix_pair`) and do the means in the kernel that adds."""
+
+    def __init__(self, dim: int, left: Mixer, right: Mixer, norm_eps: float, names: Dict[str, str]):
+        super().__init__(names)
+        self.dim, self.left, self.right, self.eps = dim, left, right, float(norm_eps)
+        self.left_out = self.right_out = None
+
+    def children(self):
+        return (self.left, self.right)
+
+    @property
+    def graph_safe(self) -> bool:
+        return bool(getattr(self.left, "graph_safe", False) and getattr(self.right, "graph_safe", False))
+
+    def local_specs(self):
+        return {"left_out": TensorSpec((self.dim,), NORM), "right_out": TensorSpec((self.dim,), NORM)}
+
+    def cache_spec(self):
+        return (self.left.cache_spec(), self.right.cache_spec())
+
+    def mix_pair(self, ctx, h, a, b, cache_layers, write_cache=True) -> None:
+        """a = left(h), b = right(h), both 32-bit [T, dim]."""
+        rows32 = ctx.memo.get(("rows32", id(h)))
+        self.left.mix(ctx, h, a, cache_layers[0], write_cache)
+        if rows32 is not None:
+            ctx.memo[("rows32", id(h))] = rows32
+        self.right.mix(ctx, h, b, cache_layers[1], write_cache)
+
+    def mix(self, ctx, h, out, cache_layers, write_cache=True) -> None:
+        a = ctx.empty(tuple(out.shape), torch.float32)
+        b = ctx.empty(tuple(out.shape), torch.float32)
+        self.mix_pair(ctx, h, a, b, cache_layers, write_cache)
+        ops.pair_rms_mean(a, self.left_out, b, self.right_out, self.eps, out)
+
+    def forward(self, ctx, h, residual, cache_layers, write_cache=True) -> None:
+        raise NotImplementedError("ParallelMixers writes its result (`mix`); blocks that add a mixer's result unchanged do not use it")

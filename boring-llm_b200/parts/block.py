@@ -171,3 +171,76 @@ class GatedSandwichBlock(Part):
             ctx.memo[("normed rows", id(nxt))] = y
         after.done = True
         return None
+
+
+class PostNormBlock(Part):
+    """The norm stands BEHIND each sublayer and the sublayers read the residual stream itself:
+
+        x += norm1(mixer(x));   x += norm2(ffn(x))          (a block without a feed-forward has only the first)
+
+    `mixer_post_norm` / `ffn_post_norm` are `LayerNorm` parts without bias. The stream is 32-bit; what the sublayers'
+    products read are its rows in the activation dtype, which the kernel that adds to the stream also writes (one launch
+    for norm, residual sum and hand-over), the stream itself in the 32-bit path. A mixer that works on the 32-bit rows
+    (a token shift) finds them in the step's memo under ("rows32", id(h)). A mixer made of two (`ParallelMixers`) hands
+    its two results to the same kernel, which norms each, takes their mean, norms again and adds."""
+
+    def __init__(self, mixer, mixer_post_norm, ffn=None, ffn_post_norm=None):
+        super().__init__()
+        self.mixer, self.mixer_post_norm, self.ffn, self.ffn_post_norm = mixer, mixer_post_norm, ffn, ffn_post_norm
+        if ffn is not None and ffn_post_norm is None:
+            raise ValueError("PostNormBlock: a feed-forward needs the norm behind it")
+        for n in (mixer_post_norm, ffn_post_norm):
+            if n is not None and (not isinstance(n, LayerNorm) or n.has_bias):
+                raise ValueError("PostNormBlock: the norms behind the sublayers are layer norms without bias")
+        self.mixer_norm = None                   # nothing in front of the mixer: no product before this block may begin a norm for it
+
+    def children(self):
+        return tuple(p for p in (self.mixer, self.mixer_post_norm, self.ffn, self.ffn_post_norm) if p is not None)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    @property
+    def graph_safe(self) -> bool:
+        return bool(getattr(self.mixer, "graph_safe", False) and (self.ffn is None or getattr(self.ffn, "graph_safe", False)))
+
+    @staticmethod
+    def _rows(ctx, x):
+        """The stream's rows as the products read them."""
+        h = ctx.memo.pop(("stream rows", id(x)), None)
+        if h is None:
+            if ctx.dtype == torch.float32:
+                h = x
+            else:
+                h = ctx.empty(tuple(x.shape))
+                ops.cast_rows(x, h)
+        ctx.memo[("rows32", id(h))] = x
+        return h
+
+    def _add(self, ctx, x, a, norm, b=None, pair=None):
+        y = ctx.empty(tuple(x.shape)) if ctx.dtype != torch.float32 else None
+        if b is None:
+            ops.post_norm_residual(x, a, norm.weight, norm.eps, y)
+        else:
+            ops.post_norm_residual(x, a, norm.weight, norm.eps, y, b=b, wa=pair.left_out, wb=pair.right_out, rms_eps=pair.eps)
+        if y is not None:
+            ctx.memo[("stream rows", id(x))] = y
+
+    def forward(self, ctx, x, cache_layer, write_cache: bool = True) -> None:
+        ctx.next_norm = None
+        h = self._rows(ctx, x)
+        a = ctx.empty(tuple(x.shape), torch.float32)
+        if hasattr(self.mixer, "mix_pair"):
+            b = ctx.empty(tuple(x.shape), torch.float32)
+            self.mixer.mix_pair(ctx, h, a, b, cache_layer, write_cache)
+            self._add(ctx, x, a, self.mixer_post_norm, b, self.mixer)
+        else:
+            self.mixer.mix(ctx, h, a, cache_layer, write_cache)
+            self._add(ctx, x, a, self.mixer_post_norm)
+        ctx.memo.pop(("rows32", id(h)), None)
+        if self.ffn is None:
+            return
+        h = self._rows(ctx, x)
+        self.ffn.apply(ctx, h, a)
+        ctx.memo.pop(("rows32", id(h)), None)
+        self._add(ctx, x, a, self.ffn_post_norm)

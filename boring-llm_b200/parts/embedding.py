@@ -37,11 +37,11 @@ class Embedding(Part):
 
 class OutputHead(Part):
     """logits = y . W^T in 32-bit, no bias (src/model.br:1360-1362). Tied to an embedding: the
-    table is shared, not copied (src/model.br:686-690)."""
+    table is shared, not copied (src/model.br:686-690). `softcap` c > 0: logits <- c * tanh(logits / c)."""
 
-    def __init__(self, vocab: int, dim: int, names: Dict[str, str], tied_to: Optional[Embedding] = None):
+    def __init__(self, vocab: int, dim: int, names: Dict[str, str], tied_to: Optional[Embedding] = None, softcap: float = 0.0):
         super().__init__(names)
-        self.vocab, self.dim, self.tied_to = vocab, dim, tied_to
+        self.vocab, self.dim, self.tied_to, self.softcap = vocab, dim, tied_to, float(softcap)
         self.weight: Optional[torch.Tensor] = None
 
     def local_specs(self):
@@ -66,9 +66,13 @@ class OutputHead(Part):
             return None
         logits = ctx.empty((row_idx.shape[0], self.vocab), torch.float32)
         ops.norm_gemm(x, norm.weight, norm.eps, self.matrix(), logits, None, EPI_NONE, row_idx)
+        if self.softcap > 0:
+            ops.softcap(logits, self.softcap)
         return logits
 
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
         logits = ctx.empty((y.shape[0], self.vocab), torch.float32)
         linear(ctx, y, self.matrix(), logits, None, EPI_NONE)
+        if self.softcap > 0:
+            ops.softcap(logits, self.softcap)
         return logits

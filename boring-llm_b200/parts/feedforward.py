@@ -6,7 +6,7 @@ from typing import Dict
 import torch
 
 from ..kernels import ops
-from ..weights import TensorSpec, MATRIX
+from ..weights import TensorSpec, MATRIX, BIAS
 from .base import Part, to_device_matrix
 from .linear import linear, EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU
 
@@ -118,3 +118,69 @@ class SwiGLU(FeedForward):
         act = ctx.empty((h.shape[0], self.hidden))
         linear(ctx, h, self.w_gate_up, act, None, EPI_SWIGLU)
         linear(ctx, act, self.w_down, residual, None, EPI_RESIDUAL)
+
+
+class RoutedExperts(FeedForward):
+    """A mixture of experts: `n_experts` small SwiGLU feed-forwards without biases, of which each token uses `top`.
+
+    Router logits z = h Wr^T in 32-bit, scores s = sigmoid(z). The CHOICE runs on s + correction (a learned vector), the
+    weights are the chosen experts' s as they are (not renormalised). The experts form `n_groups` equal runs of
+    neighbours; a group's score is the sum of its two largest choice scores, and only experts of the `keep_groups` best
+    groups can be chosen. The result is the weighted sum of the chosen experts' outputs, added in the order of the choice.
+    The experts' matrices are stacked ([E, 2 * hidden, dim] gate rows then up rows, [E, dim, hidden]); every (token,
+    chosen expert) pair is a row of two products whose rows each use the matrix of their own expert."""
+    graph_safe = True
+
+    def __init__(self, dim: int, hidden: int, n_experts: int, top: int, names: Dict[str, str], n_groups: int = 1,
+                 keep_groups: int = 1, correction: bool = True):
+        super().__init__(names)
+        if n_experts % n_groups != 0 or not 1 <= keep_groups <= n_groups:
+            raise ValueError(f"RoutedExperts: {n_experts} experts in {n_groups} groups, {keep_groups} kept")
+        if not 1 <= top <= keep_groups * (n_experts // n_groups):
+            raise ValueError(f"RoutedExperts: {top} experts a token out of {keep_groups} groups of {n_experts // n_groups}")
+        self.dim, self.hidden, self.E, self.top = dim, hidden, n_experts, top
+        self.n_groups, self.keep_groups, self.has_correction = n_groups, keep_groups, bool(correction)
+        self.router = self.correction = self.w_gate_up = self.w_down = None
+
+    def local_specs(self):
+        s = {"router": TensorSpec((self.E, self.dim), MATRIX)}
+        if self.has_correction:
+            s["correction"] = TensorSpec((self.E,), BIAS)
+        for e in range(self.E):
+            s[f"gate{e}"] = TensorSpec((self.hidden, self.dim), MATRIX)
+            s[f"up{e}"] = TensorSpec((self.hidden, self.dim), MATRIX)
+            s[f"down{e}"] = TensorSpec((self.dim, self.hidden), MATRIX)
+        return s
+
+    def place(self, local, dtype, device):
+        self.router = to_device_matrix(local["router"], dtype, device)
+        if self.has_correction:
+            self.correction = local["correction"].to(device=device, dtype=torch.float32).contiguous()
+        self.w_gate_up = to_device_matrix(torch.stack([torch.cat([local[f"gate{e}"], local[f"up{e}"]], dim=0) for e in range(self.E)]),
+                                          dtype, device)
+        self.w_down = to_device_matrix(torch.stack([local[f"down{e}"] for e in range(self.E)]), dtype, device)
+
+    def route(self, ctx, h):
+        """(experts [T, top] int32, weights [T, top] 32-bit) of the rows h."""
+        T = h.shape[0]
+        z = ctx.empty((T, self.E), torch.float32)
+        ops.gemm_plain(h, self.router, z, None, EPI_NONE)          # 32-bit sums in a fixed order, whatever the step's rows
+        ids = torch.empty((T, self.top), dtype=torch.int32, device=ctx.device)
+        wts = ctx.empty((T, self.top), torch.float32)
+        ops.moe_route(z, self.correction, self.top, self.n_groups, self.keep_groups, ids, wts)
+        return ids, wts
+
+    def _run(self, ctx, h, out, add):
+        T = h.shape[0]
+        ids, wts = self.route(ctx, h)
+        act = ctx.empty((T * self.top, self.hidden))
+        ops.expert_gemm_plain(h, self.top, self.w_gate_up, ids, act, EPI_SWIGLU)
+        y = ctx.empty((T * self.top, self.dim), torch.float32)
+        ops.expert_gemm_plain(act, 1, self.w_down, ids, y, EPI_NONE)
+        ops.moe_combine(y, wts, out, add=add)
+
+    def forward(self, ctx, h, residual):
+        self._run(ctx, h, residual, True)
+
+    def apply(self, ctx, h, out):
+        self._run(ctx, h, out, False)

@@ -14,10 +14,17 @@ from .base import Part, takes_pending_norm
 class LayerCall:
     """One entry of the run order: run block `block` on cache layer `cache`. A block may be named
     by several entries (its weights run twice), and an entry with `write_cache` false reads the
-    cache layer that an earlier entry wrote instead of writing one of its own."""
+    cache layer that an earlier entry wrote instead of writing one of its own. A block whose mixer
+    keeps several caches (pages AND a state slot: its `cache_spec()` is a tuple) names as many cache
+    layers, as a tuple."""
     block: int
-    cache: Optional[int]
+    cache: Optional[object]          # int, or a tuple of ints for a block with several caches
     write_cache: bool = True
+
+    def cache_layers(self) -> tuple:
+        if self.cache is None:
+            return ()
+        return tuple(self.cache) if isinstance(self.cache, (tuple, list)) else (self.cache,)
 
 
 class DecoderModel(Part):
@@ -36,22 +43,40 @@ class DecoderModel(Part):
         super().__init__()
         self.embedding, self.blocks, self.final_norm, self.head = embedding, list(blocks), final_norm, head
         self.depth_mix = list(depth_mix) if depth_mix is not None else None
-        self.schedule: List[LayerCall] = list(schedule) if schedule is not None else [
-            LayerCall(i, i if b.cache_spec() is not None else None) for i, b in enumerate(self.blocks)]
+        self.schedule: List[LayerCall] = list(schedule) if schedule is not None else self._default_order()
+        self.keep_streams = None                # a list: every forward pass appends a copy of the stream behind each entry (tests)
         self.ignorable_tensors = tuple(ignorable_tensors)
         written = set()
         for call in self.schedule:
             if not 0 <= call.block < len(self.blocks):
                 raise ValueError(f"run order names block {call.block}, but there are {len(self.blocks)}")
-            if call.cache is not None:
+            for c in call.cache_layers():
                 if call.write_cache:
-                    if call.cache in written:
-                        raise ValueError(f"cache layer {call.cache} is written by two entries of the run order")
-                    written.add(call.cache)
-                elif call.cache not in written:
-                    raise ValueError(f"an entry reads cache layer {call.cache} before any entry writes it")
+                    if c in written:
+                        raise ValueError(f"cache layer {c} is written by two entries of the run order")
+                    written.add(c)
+                elif c not in written:
+                    raise ValueError(f"an entry reads cache layer {c} before any entry writes it")
         if self.depth_mix is not None and len(self.depth_mix) != len(self.schedule):
             raise ValueError(f"{len(self.depth_mix)} depth-mix parts for {len(self.schedule)} entries of the run order")
+
+    def _default_order(self) -> List[LayerCall]:
+        """Every block once, in order, each with cache layers of its own: cache layer i for block i, or, in a model with
+        blocks that keep several caches, numbered through (one per cache)."""
+        specs = [b.cache_spec() for b in self.blocks]
+        if not any(isinstance(sp, tuple) for sp in specs):
+            return [LayerCall(i, i if sp is not None else None) for i, sp in enumerate(specs)]
+        order, nxt = [], 0
+        for i, spec in enumerate(specs):
+            if spec is None:
+                order.append(LayerCall(i, None))
+            elif isinstance(spec, tuple):
+                order.append(LayerCall(i, tuple(range(nxt, nxt + len(spec)))))
+                nxt += len(spec)
+            else:
+                order.append(LayerCall(i, nxt))
+                nxt += 1
+        return order
 
     def children(self):
         return (self.embedding, *self.blocks, *(self.depth_mix or ()), self.final_norm, self.head)
@@ -67,15 +92,20 @@ class DecoderModel(Part):
 
     def cache_specs(self) -> list:
         """What each cache layer needs, indexed by cache layer (None where unused)."""
-        n = 1 + max([c.cache for c in self.schedule if c.cache is not None], default=-1)
+        n = 1 + max([c for call in self.schedule for c in call.cache_layers()], default=-1)
         specs = [None] * n
         for call in self.schedule:
-            if call.cache is None:
+            layers = call.cache_layers()
+            if not layers:
                 continue
             spec = self.blocks[call.block].cache_spec()
-            if specs[call.cache] is not None and specs[call.cache] != spec:
-                raise ValueError(f"cache layer {call.cache} is shared by layers with different needs")
-            specs[call.cache] = spec
+            each = spec if isinstance(spec, tuple) else (spec,)
+            if len(each) != len(layers):
+                raise ValueError(f"block {call.block} keeps {len(each)} caches, its entry of the run order names {len(layers)} cache layers")
+            for c, sp in zip(layers, each):
+                if specs[c] is not None and specs[c] != sp:
+                    raise ValueError(f"cache layer {c} is shared by layers with different needs")
+                specs[c] = sp
         return specs
 
     def forward(self, ctx) -> torch.Tensor:
@@ -91,6 +121,8 @@ class DecoderModel(Part):
             reader = getattr(after, "mixer", None)
             ctx.norm_after_block = getattr(after, "mixer_norm", None) if takes_pending_norm(reader, x.shape[0]) else None
             self.blocks[call.block].forward(ctx, x, call.cache, call.write_cache)
+            if self.keep_streams is not None:
+                self.keep_streams.append(x.clone())
         ctx.norm_after_block = None
         return self._logits(ctx, x)
 

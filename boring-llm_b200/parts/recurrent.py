@@ -200,3 +200,137 @@ class ChannelDeltaRule(_StateMixer):
         y = ctx.empty((T, H * dv))
         ops.head_norm_gate(o, self.norm, glog, ops.GATE_SIGMOID, self.eps, y, H, dv)
         linear(ctx, y, self.wo, out, None, epilogue)
+
+
+class MatrixMemory(_StateMixer):
+    """A matrix memory per head with exponential gates held against a running maximum (the mLSTM of xLSTM). With
+    q = h Wq^T / sqrt(key_dim), k = h Wk^T, v = h Wv^T and, per head, a log input gate i = cap tanh((h Wi^T + bi) / cap) and a
+    log forget gate f = log sigmoid(cap tanh((h Wf^T + bf) / cap)):
+
+        m' = max(f + m, i);   S' = e^(f + m - m') S + e^(i - m') k v^T;   n' = e^(f + m - m') n + e^(i - m') k
+        o = S'^T q / (max(|n' . q|, e^(-m')) + 1e-6)
+
+    S, n and m start at zero. Each head's o is divided by its root mean square, the heads are joined, multiplied by a
+    weight per head and channel and by sigmoid(h Wg^T), and projected by Wo. One joined product makes q | k | v | g | i | f;
+    a kernel walks the gates (scalars per head) and leaves decays and weighted keys, which the scan of
+    `GatedLinearAttention` consumes. The slot holds S [H, dk, dv], n [H, dk], m [H]."""
+    RULE = ops.RULE_GLA
+
+    def __init__(self, dim: int, n_heads: int, key_dim: int, value_dim: int, gate_cap: float, norm_eps: float, names: Dict[str, str]):
+        super().__init__(names)
+        self.dim, self.H, self.dk, self.dv = dim, n_heads, key_dim, value_dim
+        self.cap, self.eps = float(gate_cap), float(norm_eps)
+        H, dk, dv = self.H, self.dk, self.dv
+        self.off_k, self.off_v, self.off_g = H * dk, 2 * H * dk, 2 * H * dk + H * dv
+        self.off_i = self.off_g + H * dv
+        self.off_f = self.off_i + H
+        self.off_n, self.off_m = H * dk * dv, H * dk * dv + H * dk
+        self.w_in = self.wo = self.norm = self.bias_i = self.bias_f = None
+
+    def local_specs(self):
+        H, dk, dv, d = self.H, self.dk, self.dv, self.dim
+        return {"wq": TensorSpec((H * dk, d), MATRIX), "wk": TensorSpec((H * dk, d), MATRIX), "wv": TensorSpec((H * dv, d), MATRIX),
+                "wg": TensorSpec((H * dv, d), MATRIX), "wi": TensorSpec((H, d), MATRIX), "wf": TensorSpec((H, d), MATRIX),
+                "bias_i": TensorSpec((H,), BIAS), "bias_f": TensorSpec((H,), BIAS), "norm": TensorSpec((H * dv,), NORM),
+                "wo": TensorSpec((d, H * dv), MATRIX)}
+
+    def place(self, local, dtype, device):
+        self.w_in = to_device_matrix(torch.cat([local[n] for n in ("wq", "wk", "wv", "wg", "wi", "wf")], dim=0), dtype, device)
+        self.wo = to_device_matrix(local["wo"], dtype, device)
+        self.norm = to_device_vector(local["norm"], dtype, device)
+        self.bias_i = to_device_vector(local["bias_i"], dtype, device)
+        self.bias_f = to_device_vector(local["bias_f"], dtype, device)
+
+    def cache_spec(self):
+        return StateSpec((self.H * self.dk * self.dv + self.H * self.dk + self.H,), "float32")
+
+    def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
+        self._check(write_cache)
+        T, H, dk, dv = h.shape[0], self.H, self.dk, self.dv
+        proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
+        linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        self._joined(proj)
+        state = ctx.state(cache_layer)
+        decay = ctx.empty((T, H * dk), torch.float32)
+        keys = ctx.empty((T, H * dk), torch.float32)
+        den = ctx.empty((T, H), torch.float32)
+        ops.memory_gates(proj, 0, self.off_k, self.off_i, self.off_f, self.bias_i, self.bias_f, self.cap, dk ** -0.5, state,
+                         self.off_n, self.off_m, ctx.slots, ctx.cu_q, decay, keys, den, H, dk)
+        o = ctx.empty((T, H * dv), torch.float32)
+        ops.recurrent_scan(ops.RULE_GLA, proj[:, :self.off_k], keys, proj[:, self.off_v:self.off_g], decay, None, dk ** -0.5, state,
+                           ctx.slots, ctx.cu_q, o, H, H, dk, dv, parts=self._step_parts(ctx))
+        y = ctx.empty((T, H * dv))
+        ops.head_norm_gate_ext(o, self.norm, proj[:, self.off_g:self.off_i], ops.GATE_SIGMOID, self.eps, y, H, dv, den=den)
+        linear(ctx, y, self.wo, out, None, epilogue)
+
+
+class ShiftedDecayRecurrence(_StateMixer):
+    """A linear recurrence whose inputs are mixed with the token before (the time mixing of RWKV). With h' the row of the
+    request's token before (zeros before the first), each of r, k, v, the gate and the decay reads its own
+    h + (h' - h) * mu_s. Per head (keys and values of `head_dim`), with a bonus u per head and key channel for the
+    current token only:
+
+        o = (S + diag(u) k v^T)^T r;   S <- diag(w) S + k v^T;   w = exp(-exp(tanh(mix_w W1^T) W2^T + w0))
+
+    Each head's o is divided by its root mean square, the heads are joined, multiplied by a weight per head and channel
+    and by silu(mix_g Wg^T), and projected by Wo. The mixes are made from the 32-bit rows (the block leaves them in the
+    step's memo), the slot holds S [H, dk, dk] and h' [dim]."""
+    RULE = ops.RULE_BONUS
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, dim: int, n_heads: int, head_dim: int, norm_eps: float, names: Dict[str, str], decay_rank: Optional[int] = None):
+        super().__init__(names)
+        self.dim, self.H, self.dk, self.dv = dim, n_heads, head_dim, head_dim
+        self.eps, self.rank = float(norm_eps), decay_rank
+        self.off_prev = self.H * self.dk * self.dk
+        self.mu = self.wr = self.wk = self.wv = self.wg = self.w1 = self.w2 = self.w0 = self.u = self.norm = self.wo = None
+
+    def local_specs(self):
+        H, dk, d = self.H, self.dk, self.dim
+        r = -1 if self.rank is None else self.rank
+        s = {f"mu_{m}": TensorSpec((d,), NORM) for m in self.MIXES}
+        s.update({"wr": TensorSpec((H * dk, d), MATRIX), "wk": TensorSpec((H * dk, d), MATRIX), "wv": TensorSpec((H * dk, d), MATRIX),
+                  "wg": TensorSpec((H * dk, d), MATRIX), "w1": TensorSpec((r, d), MATRIX), "w2": TensorSpec((H * dk, r), MATRIX),
+                  "w0": TensorSpec((H * dk,), BIAS), "u": TensorSpec((H, dk), MATRIX), "norm": TensorSpec((H * dk,), NORM),
+                  "wo": TensorSpec((d, H * dk), MATRIX)})
+        return s
+
+    def place(self, local, dtype, device):
+        self.rank = _rank(local["w1"], local["w2"], "the decay's factors")
+        self.mu = torch.stack([local[f"mu_{m}"].to(torch.float32) for m in self.MIXES], dim=0).to(device).contiguous()
+        for n in ("wr", "wk", "wv", "wg", "w1", "w2", "wo"):
+            setattr(self, n, to_device_matrix(local[n], dtype, device))
+        self.w0 = to_device_vector(local["w0"], dtype, device)
+        self.norm = to_device_vector(local["norm"], dtype, device)
+        self.u = local["u"].to(device=device, dtype=torch.float32).contiguous()
+
+    def cache_spec(self):
+        return StateSpec((self.H * self.dk * self.dk + self.dim,), "float32")
+
+    def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
+        self._check(write_cache)
+        x32 = h if h.dtype == torch.float32 else ctx.memo.get(("rows32", id(h)))
+        if x32 is None:
+            raise TypeError("ShiftedDecayRecurrence mixes its inputs in 32-bit: the block must leave the 32-bit rows that `h` was made "
+                            "from in the step's memo under ('rows32', id(h))")
+        T, H, dk = h.shape[0], self.H, self.dk
+        state = ctx.state(cache_layer)
+        prev = state[:, self.off_prev:]
+        mixes = ctx.empty((len(self.MIXES), T, self.dim))
+        ops.shift_mix(x32, self.mu, prev, ctx.slots, ctx.tok_req, ctx.cu_q, mixes)
+        ops.conv_tail_update(x32, 2, prev, ctx.slots, ctx.cu_q, self.dim)
+        r, k, v, g = (ctx.empty((T, H * dk), torch.float32) for _ in range(4))
+        for i, (w, dst) in enumerate(((self.wr, r), (self.wk, k), (self.wv, v), (self.wg, g))):
+            linear(ctx, mixes[i], w, dst, None, EPI_NONE)
+        low = ctx.empty((T, self.rank), torch.float32)
+        linear(ctx, mixes[4], self.w1, low, None, EPI_NONE)
+        decay = ctx.empty((T, H * dk), torch.float32)
+        ops.gemm_plain_decay_exp(low, self.w2, self.w0, decay, x_tanh=True)
+        bonus = ctx.empty((T, H), torch.float32)
+        ops.bonus_dot(r, k, self.u, bonus, H, dk)
+        o = ctx.empty((T, H * dk), torch.float32)
+        ops.recurrent_scan(ops.RULE_BONUS, r, k, v, decay, bonus, 1.0, state, ctx.slots, ctx.cu_q, o, H, H, dk, dk,
+                           parts=self._step_parts(ctx))
+        y = ctx.empty((T, H * dk))
+        ops.head_norm_gate_ext(o, self.norm, g, ops.GATE_SILU, self.eps, y, H, dk)
+        linear(ctx, y, self.wo, out, None, epilogue)
