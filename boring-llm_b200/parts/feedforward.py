@@ -141,6 +141,7 @@ class RoutedExperts(FeedForward):
         self.dim, self.hidden, self.E, self.top = dim, hidden, n_experts, top
         self.n_groups, self.keep_groups, self.has_correction = n_groups, keep_groups, bool(correction)
         self.router = self.correction = self.w_gate_up = self.w_down = None
+        self.record = None               # a list: every step appends a copy of the experts it chose [T, top] (tests; kernels launched singly)
 
     def local_specs(self):
         s = {"router": TensorSpec((self.E, self.dim), MATRIX)}
@@ -168,6 +169,8 @@ class RoutedExperts(FeedForward):
         ids = torch.empty((T, self.top), dtype=torch.int32, device=ctx.device)
         wts = ctx.empty((T, self.top), torch.float32)
         ops.moe_route(z, self.correction, self.top, self.n_groups, self.keep_groups, ids, wts)
+        if self.record is not None:
+            self.record.append(ids.clone())
         return ids, wts
 
     def _run(self, ctx, h, out, add):

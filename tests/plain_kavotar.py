@@ -174,7 +174,13 @@ def route(h, router, correction, top, groups, keep):
     """Returns (experts [T, top], weights [T, top]): scores sigmoid(h router^T); the choice runs on score + correction,
     among the experts of the `keep` groups (of `groups` equal runs of neighbours) whose two largest choice scores add up
     highest; the weights are the scores themselves, as they are."""
-    s = torch.sigmoid(h @ router.T)
+    return route_from_logits(h @ router.T, correction, top, groups, keep)
+
+
+def route_from_logits(z, correction, top, groups, keep, margins=False):
+    """With `margins` also returns, per token, how far the choice is from another one: the smaller of the gap between the
+    last chosen and the best unchosen open expert and the gap between the last kept and the best closed group."""
+    s = torch.sigmoid(z)
     choice = s + correction
     T, E = s.shape
     per = E // groups
@@ -185,12 +191,29 @@ def route(h, router, correction, top, groups, keep):
     allowed.scatter_(1, kept, True)
     masked = choice.masked_fill(~allowed[:, :, None].expand(T, groups, per).reshape(T, E), float("-inf"))
     idx = masked.topk(top, dim=-1).indices
-    return idx, s.gather(1, idx)
+    if not margins:
+        return idx, s.gather(1, idx)
+    margin = torch.full((T,), float("inf"), dtype=F64)
+    if top < keep * per:
+        best = masked.topk(top + 1, dim=-1).values
+        margin = torch.minimum(margin, best[:, top - 1] - best[:, top])
+    if keep < groups:
+        best = gscore.topk(keep + 1, dim=-1).values
+        margin = torch.minimum(margin, best[:, keep - 1] - best[:, keep])
+    return idx, s.gather(1, idx), margin
 
 
-def routed_experts(h, w, c):
-    """c: experts, top, groups, keep; w: 'router', 'correction', 'e<j>.gate' / '.up' / '.down'."""
-    idx, wt = route(h, w["router"], w["correction"], c["top"], c["groups"], c["keep"])
+def routed_experts(h, w, c, forced=None, info=None):
+    """c: experts, top, groups, keep; w: 'router', 'correction', 'e<j>.gate' / '.up' / '.down'. `forced` [T, top]: experts
+    to use instead of the own choice (their weights are still the own scores); `info`: a list that receives (own choice,
+    margin of the own choice)."""
+    z = h @ w["router"].T
+    idx, wt, margin = route_from_logits(z, w["correction"], c["top"], c["groups"], c["keep"], margins=True)
+    if info is not None:
+        info.append((idx, margin))
+    if forced is not None:
+        idx = torch.as_tensor(forced, dtype=torch.long)
+        wt = torch.sigmoid(z).gather(1, idx)
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=F64)
     for t in range(h.shape[0]):
         for j in range(c["top"]):
@@ -211,9 +234,10 @@ def _mixer_sizes(layer):
             "right": m["right"]}
 
 
-def forward(config: dict, tensors: dict, tokens, streams: bool = False):
+def forward(config: dict, tensors: dict, tokens, streams: bool = False, forced=None, info=None):
     """Logits [T, vocab] of one sequence from its start (and, with `streams`, the residual stream after every layer
-    [layers, T, width])."""
+    [layers, T, width]). `forced` {layer: experts [T, top]}: the experts to use in that layer's feed-forward; `info` {}:
+    receives {layer: (own choice, margin)}."""
     W = {n: t.to(F64) for n, t in tensors.items()}
     eps = float(config["norm"]["eps"])
     x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)]
@@ -232,7 +256,11 @@ def forward(config: dict, tensors: dict, tokens, streams: bool = False):
         if layer.get("mlp") is not None:
             r = layer["mlp"]["router"]
             w = {n[len(p) + 4:]: t for n, t in W.items() if n.startswith(p + "mlp.")}
-            y = routed_experts(x, w, dict(experts=r["experts"], top=r["top"], groups=r["groups"]["count"], keep=r["groups"]["keep"]))
+            got = []
+            y = routed_experts(x, w, dict(experts=r["experts"], top=r["top"], groups=r["groups"]["count"], keep=r["groups"]["keep"]),
+                               forced=None if forced is None else forced.get(i), info=got)
+            if info is not None:
+                info[i] = got[0]
             x = x + layer_norm(y, W[p + "norm2"], eps)
         kept.append(x)
     logits = layer_norm(x, W["final.norm"], eps) @ W["head"].T
