@@ -6,6 +6,7 @@ its roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--sizes 0.5b|3b|7b] [--layers L]
     python bench.py --design fezopel [--sizes 0.5b|3b] [--layers L]     # another design beside Qwen2 at equal sizes (its own JSON line)
+    python bench.py --design kavotar [--sizes 0.5b|3b] [--layers L]     # the Kavotar design beside Fezopel and Qwen2 at equal sizes
 
 One JSON line on standard output. A "step" is one decode step of the whole batch. Requests are real ones: random
 prompts admitted by the scheduler, prefilled in portions through the engine, then decoded; the model comes from the
@@ -362,6 +363,34 @@ def fezopel_config(sizes, n_layers):
                                       "max_position_embeddings": 32768})
 
 
+KAVOTAR_CHUNK = 1024
+KAVOTAR_PATTERN = ("mlstm", "parallel")                           # repeated over the layers
+KAVOTAR_EXPERTS, KAVOTAR_TOP, KAVOTAR_GROUPS, KAVOTAR_KEEP = 16, 4, 4, 2
+
+
+def kavotar_config(sizes, n_layers):
+    """A Kavotar model with the width, heads, head size, layers and vocabulary of a Qwen2.5 size: the matrix memory has half
+    the heads with values twice as wide (its output projection has the attention's shape), the parallel layer's attention
+    has the Qwen2 heads inside chunks of 1,024 positions and its recurrence heads x head size = width; every layer has 16
+    experts of a quarter of the dense feed-forward's hidden size, 4 a token (the arithmetic of the dense feed-forward, four
+    times its weights)."""
+    import boring_llm_b200 as b
+    s = SIZES[sizes]
+    d, H, KV, dh, F, V = (s[k] for k in ("hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
+                                         "intermediate_size", "vocab_size"))
+    mixers = {
+        "mlstm": {"heads": H // 2, "dim": dh, "vdim": 2 * dh, "gate_cap": 15.0},
+        "parallel": {"left": {"heads": H, "kv_heads": KV, "dim": dh, "vdim": dh, "mask": {"size": KAVOTAR_CHUNK},
+                              "rot": {"base": 1000000.0, "dims": dh // 2}, "scale": dh ** -0.5},
+                     "right": {"heads": d // dh, "dim": dh, "rank": 32}},
+    }
+    mlp = {"kind": "moe", "expert": {"ff": F // KAVOTAR_TOP // 8 * 8},
+           "router": {"experts": KAVOTAR_EXPERTS, "top": KAVOTAR_TOP, "groups": {"count": KAVOTAR_GROUPS, "keep": KAVOTAR_KEEP}}}
+    layers = [{"type": t, "mixer": mixers[t], "mlp": mlp} for t in (KAVOTAR_PATTERN[i % len(KAVOTAR_PATTERN)] for i in range(n_layers))]
+    return b.KavotarConfig.from_dict({"architecture": "Kavotar", "vocab": V, "width": d, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+                                      "layers": layers, "max_position_embeddings": 32768})
+
+
 def kernel_time_line(eng, entries, again):
     """The time of every kernel of one step INSIDE its captured graph: the step is captured with a time stamp between
     every two kernels, then `again` (the same shape: it replays that graph) runs, and the stamps of the replay give
@@ -394,7 +423,8 @@ def kernel_time_line(eng, entries, again):
 
 
 def design_bench(args):
-    """Prefill and decode of the Fezopel design beside Qwen2 at equal sizes, random weights, bfloat16: one JSON line."""
+    """Prefill and decode of another design (Fezopel; Kavotar) beside the models it is compared with at equal sizes, random
+    weights, bfloat16: one JSON line."""
     import gc
     import torch
     import boring_llm_b200 as b
@@ -403,14 +433,19 @@ def design_bench(args):
     from boring_llm_b200.engine.runner import StepEntry
     pk = peaks()
     n_layers = args.layers or 8
-    out = {"design": "fezopel", "beside": "qwen2", "sizes": args.sizes, "layers": n_layers, "dtype": "bf16", "data": "synthetic",
-           "pattern": list(FEZOPEL_PATTERN), "window": FEZOPEL_WINDOW, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
-           "peaks": pk["source"], "models": {}}
+    makers = {"fezopel": fezopel_config, "kavotar": kavotar_config,
+              "qwen2": lambda sizes, n: b.Qwen2Config.from_dict({**COMMON, **SIZES[sizes], "num_hidden_layers": n})}
+    names = ("fezopel", "qwen2") if args.design == "fezopel" else ("kavotar", "fezopel", "qwen2")
+    out = {"design": args.design, "beside": list(names[1:]), "sizes": args.sizes, "layers": n_layers, "dtype": "bf16", "data": "synthetic",
+           "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "peaks": pk["source"], "models": {}}
+    if args.design == "fezopel":
+        out.update(beside="qwen2", pattern=list(FEZOPEL_PATTERN), window=FEZOPEL_WINDOW)
+    else:
+        out.update(pattern=list(KAVOTAR_PATTERN), chunk=KAVOTAR_CHUNK, experts=[KAVOTAR_EXPERTS, KAVOTAR_TOP, KAVOTAR_GROUPS, KAVOTAR_KEEP])
     clocks = ClockSampler()
     clocks.start()
-    for name in ("fezopel", "qwen2"):
-        cfg = (fezopel_config(args.sizes, n_layers) if name == "fezopel"
-               else b.Qwen2Config.from_dict({**COMMON, **SIZES[args.sizes], "num_hidden_layers": n_layers}))
+    for name in names:
+        cfg = makers[name](args.sizes, n_layers)
         opts = EngineOptions(dtype="bfloat16", ctx_size=CONTEXT, max_num_seqs=64, max_tokens=(CONTEXT + 16) * 64,
                              max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk=PORTION, cuda_graphs=not args.no_graphs)
         eng = Engine.from_random(cfg, 0, opts)
@@ -470,7 +505,7 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "prefill4", "mixed"],
                     help="run one part only and print its figures (for profilers; not the benchmark line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--design", default="", choices=["", "fezopel"],
+    ap.add_argument("--design", default="", choices=["", "fezopel", "kavotar"],
                     help="measure another design beside Qwen2 at equal sizes instead of the default workload (its own JSON line)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -290,20 +290,23 @@ int bl_conv_silu_unit(const float* x, int ld, const float* taps, int n_taps, con
 int bl_conv_tail_update(const float* x, int ld, int n_taps, float* tail, long long slot_stride, const int* slots,
                         const int* cu_q, int R, int C, void* stream);
 
-// bl_head_norm_gate with two options: w_per_head != 0: w holds H * dv values (a weight per head and channel); den
-// (null: none) [T, H]: o[t, h, :] is divided by den[t, h] before the norm.
-int bl_head_norm_gate_ext(const float* o, const void* w, int w_dtype, int w_per_head, const float* den, const float* gate,
-                          int ld_gate, int gate_kind, void* y, int y_dtype, int T, int H, int dv, float eps, void* stream);
-// The gates of a matrix memory with exponential gating, the tokens of each request in order. proj [T, ld] holds q at
-// off_q and k at off_k (H * dk each) and the gates' pre-activations at off_i and off_f (H each). Per token and head:
-// i = cap tanh((zi + bias_i) / cap), f = log sigmoid(cap tanh((zf + bias_f) / cap)), m' = max(f + m, i), a = e^(f + m - m'),
-// e = e^(i - m'), n' = a n + e k, den = max(|n' . q| q_scale, e^(-m')) + 1e-6. a_out [T, H * dk] (a for every key channel
-// of the head: the decays bl_recurrent_scan reads), k_out [T, H * dk] = e k, den_out [T, H]. n [H, dk] and m [H] are kept
-// in the request's slot at off_n and off_m (floats from the slot's start); a zeroed slot is the start of a sequence.
-int bl_memory_gates(const float* proj, int ld, int off_q, int off_k, int off_i, int off_f, const void* bias_i, int bi_dtype,
-                    const void* bias_f, int bf_dtype, float cap, float q_scale, float* state, long long slot_stride,
-                    long long off_n, long long off_m, const int* slots, const int* cu_q, int R, float* a_out, float* k_out,
-                    float* den_out, int H, int dk, void* stream);
+// bl_head_norm_gate with options: the heads of a row of o lie o_head_stride values apart; w_per_head != 0: w holds H * dv
+// values (a weight per head and channel); floor (null: none) [T, H]: o[t, h, :dv] is divided by
+// max(|o[t, h, dv]|, floor[t, h]) + 1e-6 before the norm (o_head_stride >= dv + 1).
+int bl_head_norm_gate_ext(const float* o, int o_head_stride, const void* w, int w_dtype, int w_per_head, const float* floor,
+                          const float* gate, int ld_gate, int gate_kind, void* y, int y_dtype, int T, int H, int dv, float eps,
+                          void* stream);
+// The gates of a matrix memory with exponential gating, the tokens of each request in order. proj [T, ld] holds k at
+// off_k (H * dk), v at off_v (H * dv) and the gates' pre-activations at off_i and off_f (H each). Per token and head:
+// i = cap tanh((zi + bias_i) / cap), f = log sigmoid(cap tanh((zf + bias_f) / cap)), m' = max(f + m, i) (m [H] is kept in
+// the request's slot at off_m floats from its start; a zeroed slot is the start of a sequence), a = e^(f + m - m'),
+// e = e^(i - m'). gates [3, T, H]: a, e, e^(-m'). What bl_recurrent_scan (BL_RULE_GLA, value size dv + 1) then reads:
+// decay [T, H * dk] = a for every key channel, k_out [T, H * dk] = e k, v_out [T, H * (dv + 1)] = (v, 1): the state's last
+// value column is the normaliser n' = a n + e k, the read-out's last column n' . q.
+int bl_memory_gates(const float* proj, int ld, int off_k, int off_v, int off_i, int off_f, const void* bias_i, int bi_dtype,
+                    const void* bias_f, int bf_dtype, float cap, float* state, long long slot_stride, long long off_m,
+                    const int* slots, const int* cu_q, int R, int T, float* gates, float* decay, float* k_out, float* v_out,
+                    int H, int dk, int dv, void* stream);
 // out[s, t, :] = x[t, :] + (x'[t, :] - x[t, :]) * mu[s, :], s < n_mix, x' the row of the request's token before; for a
 // step's first token of a request it is prev + slots[r] * slot_stride [d] (bl_conv_tail_update with two taps keeps it).
 int bl_shift_mix(const float* x, int ld, const void* mu, int mu_dtype, int n_mix, const float* prev, long long slot_stride,
@@ -314,12 +317,13 @@ int bl_bonus_dot(const float* q, int ldq, const float* k, int ldk, const void* u
 
 // bl_qk_norm_rope_write with the norm's scope as an argument: per_head 0: one RMS norm over a token's whole q row (weights
 // [H * dk]) and one over its whole k row ([KV * dk]); per_head != 0: a norm over each head's dk values, the weights [dk]
-// shared by the heads.
+// shared by the heads. q_head_scale (null: none): 32-bit [H], head h of q is multiplied by q_head_scale[h] as it is written
+// (a factor per head on the scores, of either sign, costs the attention kernels nothing this way).
 int bl_qk_norm_rope_write_scope(const float* proj, int ld, int off_k, int off_v, const void* q_norm_w, int qw_dtype,
                                 const void* k_norm_w, int kw_dtype, float eps, int per_head, const int* positions,
                                 const int* tok_req, const int* block_table, int max_pages, const float* inv_freq,
                                 int rot_half, int pair_layout, void* q_out, void* k_cache, void* v_cache, int dtype, int T,
-                                int H, int KV, int dk, int dv, int page_size, void* stream);
+                                int H, int KV, int dk, int dv, int page_size, const float* q_head_scale, void* stream);
 // out[m, n] = exp(-exp(u[m, :] . W[n, :] + bias[n])), u = tanh(x) where x_tanh != 0 (x: 32-bit rows ldx apart).
 int bl_gemm_plain_decay_exp(const float* x, int ldx, int x_tanh, const void* w, int w_dtype, const void* bias, int bias_dtype,
                             float* out, int M, int N, int K, void* stream);
@@ -343,7 +347,17 @@ int bl_attention_talk_plain(const void* q, const void* k_cache, const void* v_ca
                             const int* cu_q, const int* ctx_len, const int* block_table, int max_pages, float* A, int T, int H,
                             int KV, int dh, int dv, int page_size, int chunk, int window, float scale, const void* head_scale,
                             int hs_dtype, void* stream);
-int bl_talk_mix(const float* A, const void* talk, int talk_dtype, void* out, int out_dtype, int T, int H, int KV, int dv, void* stream);
+int bl_talk_mix(const void* A, int a_dtype, const void* talk, int talk_dtype, void* out, int out_dtype, int T, int H, int KV, int dv,
+                void* stream);
+// The same on tensor cores (attention_mma.cu: bfloat16, pages of 16, head sizes 16/32/48/64/96/128, values of the keys'
+// head size, positive head_scale in 32-bit): tiles / reqs as bl_attention_prefill / bl_attention_decode (up to 16 slices,
+// merged inside clusters); spread [T, H, KV, dh] bfloat16.
+int bl_attention_prefill_talk(const void* q, const void* k_cache, const void* v_cache, const int* cu_q, const int* ctx_len,
+                              const int* block_table, int max_pages, const int* tiles, int n_tiles, void* spread, int H, int KV,
+                              int dh, int page_size, int chunk, int window, float scale, const float* head_scale, void* stream);
+int bl_attention_decode_talk(const void* q, const void* k_cache, const void* v_cache, const int* cu_q, const int* ctx_len,
+                             const int* block_table, int max_pages, const int* reqs, int n, int n_splits, void* spread, int H,
+                             int KV, int dh, int page_size, int chunk, int window, float scale, const float* head_scale, void* stream);
 
 // Routed experts (moe.cu). bl_moe_route: z [T, ldz] 32-bit router logits; s = sigmoid(z), choice = s + correction (null:
 // none); experts in n_groups runs of neighbours, a group's score the sum of its two largest choice scores, the `keep` best
@@ -355,6 +369,16 @@ int bl_moe_route(const float* z, int ldz, const void* correction, int corr_dtype
 int bl_expert_gemm_plain(const void* x, int x_dtype, int x_div, const void* w, int w_dtype, long long expert_stride, const int* ids,
                          void* out, int out_dtype, int P, int N, int K, int epilogue, void* stream);
 int bl_moe_combine(const float* y, const float* wts, float* out, int T, int top, int d, int add, void* stream);
+// The same on tensor cores: the pairs (token, chosen expert) are laid out expert by expert in tiles of `tile` rows
+// (bl_moe_plan: pos [P] the row of each pair, row_src [max_tiles * tile] the pair of each row or -1, tile_expert
+// [max_tiles] the expert of each tile or -1; max_tiles >= ceil(P / tile) + E), the tokens' rows are gathered there
+// (bl_gather_rows, bfloat16 rows of a multiple of 8 values), bl_gemm_tc_grouped multiplies every tile of 128 rows by its
+// expert's matrix (gemm_tcgen05.cu), and bl_moe_combine_rows adds up a token's rows y[pos[t * top + k]].
+int bl_moe_plan(const int* ids, int P, int E, int tile, int max_tiles, int* pos, int* row_src, int* tile_expert, void* stream);
+int bl_gather_rows(const void* x, const int* row_src, int div, void* dst, int rows, int cols, void* stream);
+int bl_gemm_tc_grouped(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int epilogue, int n_experts,
+                       const int* tile_expert, void* stream);
+int bl_moe_combine_rows(const float* y, const int* pos, const float* wts, float* out, int T, int top, int d, int add, void* stream);
 
 #ifdef __cplusplus
 }

@@ -35,7 +35,17 @@ struct AttnParams {
     int* counters;                // decode with slices: one per (request, head group), zero between launches
     int H, KV, window; float scale_log2;
     BlAttnTail tail;              // a sink per head and a gate per (token, head), or nulls
+    // Options of attention whose heads are mixed after the softmax (all zero / null: plain attention).
+    int chunk;                    // > 0: position i sees only keys from i - i % chunk on
+    const float* head_scale;      // a positive factor per head on the scores' scale
+    int v_shift;                  // the values come from key/value head (kv head + v_shift) % KV instead of the keys' own
+    int spread;                   // != 0: out is [tokens, H, KV, DH] and this launch writes the entries of its value head
 };
+
+// Where the output of (token, head) goes: [tokens, H, DH], or, spread over the value heads, [tokens, H, KV, DH].
+__device__ __forceinline__ __nv_bfloat16* out_row(const AttnParams& p, size_t tok, int head, int vh, int dh) {
+    return p.out + (p.spread ? ((tok * p.H + head) * p.KV + vh) : (tok * p.H + head)) * dh;
+}
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -103,13 +113,14 @@ struct Tiles {
 // Decode: one warp copies the page of keys [key0, key0 + 16) of one key/value head, and its values, into a stage
 // of its own. A page outside [lo, hi] or no longer in the table, and keys past hi, become zeros (see load_block).
 template <int DH>
-__device__ __forceinline__ void load_page(__nv_bfloat16* stage, const AttnParams& p, const int* table, int kvh,
+__device__ __forceinline__ void load_page(__nv_bfloat16* stage, const AttnParams& p, const int* table, int kvh, int vh,
                                           int key0, int lo, int hi) {
     constexpr int CH = DH / 8;
     constexpr int ROW = Tiles<DH>::ROW;
     const int lane = threadIdx.x & 31;
     const int page = (key0 + PAGE - 1 >= lo && key0 <= hi) ? table[key0 / PAGE] : -1;
     const size_t base = page >= 0 ? ((size_t)page * p.KV + kvh) * (PAGE * DH) : 0;
+    const size_t v_base = page >= 0 ? ((size_t)page * p.KV + vh) * (PAGE * DH) : 0;
 #pragma unroll
     for (int it = 0; it < (PAGE * CH + 31) / 32; ++it) {
         const int i = lane + 32 * it;
@@ -119,7 +130,7 @@ __device__ __forceinline__ void load_page(__nv_bfloat16* stage, const AttnParams
         __nv_bfloat16* vd = kd + PAGE * ROW;
         if (page >= 0 && key0 + row <= hi) {
             cp_async16(kd, p.kc + base + i * 8);
-            cp_async16(vd, p.vc + base + i * 8);
+            cp_async16(vd, p.vc + v_base + i * 8);
         } else {
             *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
             *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
@@ -132,7 +143,7 @@ __device__ __forceinline__ void load_page(__nv_bfloat16* stage, const AttnParams
 // Pages outside [lo, hi] or no longer in the table, and keys past hi on the last page, become zeros: they are
 // masked anyway, and zeros keep the value product finite whatever an old request left in a reused page.
 template <int DH>
-__device__ __forceinline__ void load_block(__nv_bfloat16* stage, const AttnParams& p, const int* table, int kvh,
+__device__ __forceinline__ void load_block(__nv_bfloat16* stage, const AttnParams& p, const int* table, int kvh, int vh,
                                            int key0, int lo, int hi) {
     constexpr int CH = DH / 8;                                    // 16-byte chunks per row
     constexpr int CPP = PAGE * CH;                                // chunks per page
@@ -158,7 +169,7 @@ __device__ __forceinline__ void load_block(__nv_bfloat16* stage, const AttnParam
         if (page >= 0 && key0 + r <= hi) {
             const size_t off = ((size_t)page * p.KV + kvh) * (PAGE * DH) + j * 8;
             cp_async16(kd, p.kc + off);
-            cp_async16(vd, p.vc + off);
+            cp_async16(vd, p.vc + off + (size_t)(vh - kvh) * (PAGE * DH));
         } else {
             *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
             *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
@@ -170,8 +181,8 @@ __device__ __forceinline__ void load_block(__nv_bfloat16* stage, const AttnParam
 template <int DH, int NT, int KROWS = KB>
 __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff, int key_abs0,
                                            const unsigned (&qf)[DH / 16][4], float (&o)[DH / 8][4],
-                                           float (&m)[2], float (&l)[2], const int (&pos)[2], int window,
-                                           float scale_log2) {
+                                           float (&m)[2], float (&l)[2], const int (&pos)[2], const int (&lo_row)[2],
+                                           const float (&scale_log2)[2]) {
     constexpr int ROW = Tiles<DH>::ROW;
     const __nv_bfloat16* ks = stage;
     const __nv_bfloat16* vs = stage + KROWS * ROW;
@@ -195,7 +206,7 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
     float mx[2] = {-INFINITY, -INFINITY};
     // most blocks lie wholly inside what both rows may see: no per-key test there
     const int k_first = key_abs0 + koff, k_last = k_first + NT * 8 - 1;
-    const bool all_seen = k_last <= min(pos[0], pos[1]) && (window <= 0 || k_first + window > max(pos[0], pos[1]));
+    const bool all_seen = k_last <= min(pos[0], pos[1]) && k_first >= max(lo_row[0], lo_row[1]);
     if (all_seen) {
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
@@ -209,7 +220,7 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
             for (int c = 0; c < 4; ++c) {
                 const int j = k_first + n * 8 + 2 * t + (c & 1);
                 const int p = pos[c >> 1];
-                const bool seen = j <= p && (window <= 0 || j + window > p);
+                const bool seen = j <= p && j >= lo_row[c >> 1];
                 const float v = seen ? s[n][c] : -INFINITY;
                 s[n][c] = v;
                 mx[c >> 1] = fmaxf(mx[c >> 1], v);
@@ -221,7 +232,7 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
     for (int h = 0; h < 2; ++h) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-        const float m_new = fmaxf(m[h], mx[h] * scale_log2);
+        const float m_new = fmaxf(m[h], mx[h] * scale_log2[h]);
         m_use[h] = m_new == -INFINITY ? 0.f : m_new;              // a row that has seen no key yet
         if (m_new != m[h]) {                                       // (after the first blocks the maximum seldom moves)
             const float alpha = bl_ex2(m[h] - m_use[h]);           // 2^-inf = 0 on the first block
@@ -235,7 +246,7 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
     for (int n = 0; n < NT; ++n) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const float e = bl_ex2(fmaf(s[n][c], scale_log2, -m_use[c >> 1]));   // a masked score is -inf: 2^-inf = 0
+            const float e = bl_ex2(fmaf(s[n][c], scale_log2[c >> 1], -m_use[c >> 1]));   // a masked score is -inf: 2^-inf = 0
             s[n][c] = e;
             l[c >> 1] += e;
         }
@@ -302,11 +313,23 @@ attention_mma_kernel(const AttnParams p) {
         }
         pos[h] = valid[h] ? ctx - q_len + tok[h] : -1;            // an invalid row sees nothing
     }
+    // the first key each row sees (a window, a chunk of positions counted from 0, or both), and the rows' scales
+    int lo_row[2];
+    float sc_row[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int lr = p.window > 0 ? pos[h] - p.window + 1 : 0;
+        if (p.chunk > 0 && pos[h] >= 0) lr = max(lr, pos[h] - pos[h] % p.chunk);
+        lo_row[h] = max(lr, 0);
+        sc_row[h] = p.head_scale ? p.scale_log2 * p.head_scale[min(head[h], p.H - 1)] : p.scale_log2;
+    }
+    const int vh = (kvh + p.v_shift) % p.KV;                      // the key/value head whose VALUES this launch reads
     // the block's range of keys
     const int first_tok = DECODE ? 0 : tok0;
     const int last_tok = DECODE ? 0 : min(q_len, tok0 + KB) - 1;
     const int p_first = ctx - q_len + first_tok, p_last = ctx - q_len + last_tok;
-    const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    if (p.chunk > 0 && p_first >= 0) lo = max(lo, p_first - p_first % p.chunk);
     const int hi = p_last;
     int b_begin = lo / KB, b_end = hi / KB + 1;
     if (q_len <= 0) b_end = b_begin;
@@ -327,7 +350,7 @@ attention_mma_kernel(const AttnParams p) {
         // the newest token are copied into the warp's stages right away, and the rest of this slice is started on
         // its way into L2 (the newest token's row is written there by that kernel; L2 stays coherent with it).
         while (issued < WSTAGES && issued < nb && (b_begin + issued) * KB + warp * PAGE + PAGE <= hi) {
-            load_page<DH>(wring + issued * WSTAGE, p, table, kvh, (b_begin + issued) * KB + warp * PAGE, lo, hi);
+            load_page<DH>(wring + issued * WSTAGE, p, table, kvh, vh, (b_begin + issued) * KB + warp * PAGE, lo, hi);
             cp_async_commit();
             ++issued;
         }
@@ -341,7 +364,7 @@ attention_mma_kernel(const AttnParams p) {
             if (page >= 0) {
                 const size_t off = (((size_t)page * p.KV + kvh) * PAGE) * DH * 2 + (size_t)(i % LINES) * 128;
                 bl_prefetch_l2(reinterpret_cast<const char*>(p.kc) + off);
-                bl_prefetch_l2(reinterpret_cast<const char*>(p.vc) + off);
+                bl_prefetch_l2(reinterpret_cast<const char*>(p.vc) + off + (size_t)(vh - kvh) * PAGE * DH * 2);
             }
         }
     }
@@ -368,7 +391,7 @@ attention_mma_kernel(const AttnParams p) {
         // Every warp walks its own pages (page `warp` of each 64-key block) through its own ring: no barrier of the
         // block inside the loop, and up to WSTAGES pages on their way per warp.
         while (issued < WSTAGES && issued < nb) {
-            load_page<DH>(wring + issued * WSTAGE, p, table, kvh, (b_begin + issued) * KB + warp * PAGE, lo, hi);
+            load_page<DH>(wring + issued * WSTAGE, p, table, kvh, vh, (b_begin + issued) * KB + warp * PAGE, lo, hi);
             cp_async_commit();
             ++issued;
         }
@@ -378,17 +401,17 @@ attention_mma_kernel(const AttnParams p) {
             else if (pending == 1) cp_async_wait<1>(); else cp_async_wait<0>();
             __syncwarp();
             __nv_bfloat16* st = wring + (i % WSTAGES) * WSTAGE;
-            block_step<DH, 2, PAGE>(st, 0, (b_begin + i) * KB + warp * PAGE, qf, o, m, l, pos, p.window, p.scale_log2);
+            block_step<DH, 2, PAGE>(st, 0, (b_begin + i) * KB + warp * PAGE, qf, o, m, l, pos, lo_row, sc_row);
             __syncwarp();
             if (issued < nb) {                        // the stage just used takes the page WSTAGES blocks on
-                load_page<DH>(st, p, table, kvh, (b_begin + issued) * KB + warp * PAGE, lo, hi);
+                load_page<DH>(st, p, table, kvh, vh, (b_begin + issued) * KB + warp * PAGE, lo, hi);
                 cp_async_commit();
                 ++issued;
             }
         }
     } else {
         while (issued < 2 && issued < nb) {           // two blocks in flight before the first is used
-            load_block<DH>(smem + (issued & 1) * STAGE, p, table, kvh, (b_begin + issued) * KB, lo, hi);
+            load_block<DH>(smem + (issued & 1) * STAGE, p, table, kvh, vh, (b_begin + issued) * KB, lo, hi);
             cp_async_commit();
             ++issued;
         }
@@ -396,10 +419,10 @@ attention_mma_kernel(const AttnParams p) {
             const int b = b_begin + i, st = i & 1;
             if (issued - (i + 1) >= 1) cp_async_wait<1>(); else cp_async_wait<0>();   // block i has landed
             __syncthreads();
-            block_step<DH, 8>(smem + st * STAGE, 0, b * KB, qf, o, m, l, pos, p.window, p.scale_log2);
+            block_step<DH, 8>(smem + st * STAGE, 0, b * KB, qf, o, m, l, pos, lo_row, sc_row);
             __syncthreads();
             if (issued < nb) {                        // the stage just used takes the block after next
-                load_block<DH>(smem + st * STAGE, p, table, kvh, (b_begin + issued) * KB, lo, hi);
+                load_block<DH>(smem + st * STAGE, p, table, kvh, vh, (b_begin + issued) * KB, lo, hi);
                 cp_async_commit();
                 ++issued;
             }
@@ -416,7 +439,7 @@ attention_mma_kernel(const AttnParams p) {
         for (int h = 0; h < 2; ++h) {
             if (!valid[h]) continue;
             const float inv = bl_attn_tail(p.tail, m[h], l[h], (size_t)(q_begin + tok[h]), head[h]);
-            __nv_bfloat16* op = p.out + ((size_t)(q_begin + tok[h]) * p.H + head[h]) * DH + 2 * t;
+            __nv_bfloat16* op = out_row(p, (size_t)(q_begin + tok[h]), head[h], vh, DH) + 2 * t;
 #pragma unroll
             for (int n = 0; n < DH / 8; ++n)
                 *reinterpret_cast<unsigned*>(op + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
@@ -471,7 +494,7 @@ attention_mma_kernel(const AttnParams p) {
             const int hd = head0 + row;
             if (p.n_splits == 1) {
                 const float inv = bl_attn_tail(p.tail, M, L, (size_t)q_tok, hd);
-                *reinterpret_cast<uint2*>(p.out + ((size_t)q_tok * p.H + hd) * DH + d) =
+                *reinterpret_cast<uint2*>(out_row(p, (size_t)q_tok, hd, vh, DH) + d) =
                     make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
             } else if (p.part_o == nullptr) {                             // the slices are the blocks of one cluster: the partial result stays here
                 *reinterpret_cast<float4*>(cp_o + row * DH + d) = O;
@@ -514,7 +537,7 @@ attention_mma_kernel(const AttnParams p) {
                 O.x += po[s2].x * f; O.y += po[s2].y * f; O.z += po[s2].z * f; O.w += po[s2].w * f;
             }
             const float inv = bl_attn_tail(p.tail, M, L, (size_t)q_tok, head0 + row);
-            *reinterpret_cast<uint2*>(p.out + ((size_t)q_tok * p.H + head0 + row) * DH + d) =
+            *reinterpret_cast<uint2*>(out_row(p, (size_t)q_tok, head0 + row, vh, DH) + d) =
                 make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
         }
         cluster_sync_all();                                           // no block leaves while another may still read its partial result
@@ -602,7 +625,7 @@ attention_mma_kernel(const AttnParams p) {
             }
         }
         const float inv = bl_attn_tail(p.tail, sM[row], sL[row], (size_t)q_tok, head0 + row);
-        __nv_bfloat16* dst = p.out + ((size_t)q_tok * p.H + head0 + row) * DH + d;
+        __nv_bfloat16* dst = out_row(p, (size_t)q_tok, head0 + row, vh, DH) + d;
         *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
     }
 }
@@ -717,7 +740,7 @@ extern "C" int bl_attention_prefill_tail(const void* q, const void* k_cache, con
                                          void* stream) {
     if (n_tiles <= 0) return 0;
     if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
-    AttnParams p;
+    AttnParams p = {};
     p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.work = tiles; p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr; p.n_splits = 1; p.H = H; p.KV = KV; p.window = window;
@@ -753,7 +776,7 @@ extern "C" int bl_attention_decode_tail(const void* q, const void* k_cache, cons
         BL_FAIL("bl_attention_decode: slices merged through scratch memory need zeroed counters");
     if (n_splits > MAX_CLUSTER_SPLITS && scratch == nullptr)
         BL_FAIL("bl_attention_decode: more than %d slices need scratch memory and zeroed counters", MAX_CLUSTER_SPLITS);
-    AttnParams p;
+    AttnParams p = {};
     p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.work = reqs; p.n_splits = n_splits; p.H = H; p.KV = KV; p.window = window;
@@ -763,6 +786,55 @@ extern "C" int bl_attention_decode_tail(const void* q, const void* k_cache, cons
     p.tail = BlAttnTail{sinks, sink_dtype, gate, ld_gate};
     const int G = H / KV;
     return dispatch<true>(dh, p, dim3(n_splits, KV * ((G + 15) / 16), n), (cudaStream_t)stream);
+}
+
+// The same two shapes for attention whose heads' softmax weights are mixed afterwards (see attention_talk.cu): keys from
+// the query's own chunk of positions (chunk 0: all), a positive factor per head on the scale (head_scale, 32-bit, null:
+// none), and every head's softmax applied to the values of EVERY key/value head: spread [tokens, H, KV, dh] bfloat16.
+// One launch per value head (the scores are worked out again for each; the mix that follows is bl_talk_mix).
+extern "C" int bl_attention_prefill_talk(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                         const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
+                                         int n_tiles, void* spread, int H, int KV, int dh, int page_size, int chunk, int window,
+                                         float scale, const float* head_scale, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
+    if (chunk < 0) BL_FAIL("bl_attention_prefill_talk: bad chunk %d", chunk);
+    AttnParams p = {};
+    p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
+    p.out = (__nv_bfloat16*)spread; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
+    p.work = tiles; p.n_splits = 1; p.H = H; p.KV = KV; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.tail = BlAttnTail{nullptr, 0, nullptr, 0};
+    p.chunk = chunk; p.head_scale = head_scale; p.spread = 1;
+    if ((long long)n_tiles * H > 2147483647LL) BL_FAIL("bl_attention_prefill_talk: %d tiles x %d heads are more blocks than a launch takes", n_tiles, H);
+    for (int v = 0; v < KV; ++v) {
+        p.v_shift = v;
+        if (dispatch<false>(dh, p, dim3(n_tiles * H, 1, 1), (cudaStream_t)stream)) return 1;
+    }
+    return 0;
+}
+
+extern "C" int bl_attention_decode_talk(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                        const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
+                                        int n_splits, void* spread, int H, int KV, int dh, int page_size, int chunk, int window,
+                                        float scale, const float* head_scale, void* stream) {
+    if (n <= 0) return 0;
+    if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
+    if (chunk < 0) BL_FAIL("bl_attention_decode_talk: bad chunk %d", chunk);
+    if (n_splits < 1 || n_splits > MAX_CLUSTER_SPLITS) BL_FAIL("bl_attention_decode_talk: %d slices (1..%d)", n_splits, MAX_CLUSTER_SPLITS);
+    AttnParams p = {};
+    p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
+    p.out = (__nv_bfloat16*)spread; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
+    p.work = reqs; p.n_splits = n_splits; p.H = H; p.KV = KV; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.tail = BlAttnTail{nullptr, 0, nullptr, 0};
+    p.chunk = chunk; p.head_scale = head_scale; p.spread = 1;
+    const int G = H / KV;
+    for (int v = 0; v < KV; ++v) {
+        p.v_shift = v;
+        if (dispatch<true>(dh, p, dim3(n_splits, KV * ((G + 15) / 16), n), (cudaStream_t)stream)) return 1;
+    }
+    return 0;
 }
 
 // ---------------------------------------------------------------------------------------------------

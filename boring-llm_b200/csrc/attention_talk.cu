@@ -7,7 +7,8 @@
 // head's softmax is applied to the values of EVERY key/value head in one pass over the keys (online softmax, nothing of
 // size keys x keys is stored), and a small kernel mixes the heads. Chunks are counted from position 0 of the sequence.
 // This file holds the plain kernel (one warp per (token, head), any dtype: the 32-bit path and the twin of the
-// tensor-core kernel) and the mix.
+// tensor-core kernels) and the mix. On tensor cores the same is bl_attention_prefill_talk / bl_attention_decode_talk in
+// attention_mma.cu: its two shapes with a first visible key per row, a scale per head, and the values of a chosen head.
 #include "common.cuh"
 #include "api.h"
 
@@ -104,9 +105,9 @@ attention_talk_plain_kernel(const TT* __restrict__ q, const TT* __restrict__ kc,
 }
 
 // out[t, h, :] = sum_g talk[h, g] * A[t, g, kv(h), :], g ascending; one block per token.
-template <typename TT>
+template <typename TA, typename TT>
 __global__ void __launch_bounds__(128)
-talk_mix_kernel(const float* __restrict__ A, const void* __restrict__ talk, int talk_dtype, TT* __restrict__ out, int H, int KV, int dv) {
+talk_mix_kernel(const TA* __restrict__ A, const void* __restrict__ talk, int talk_dtype, TT* __restrict__ out, int H, int KV, int dv) {
     bl_pdl_trigger();
     bl_pdl_wait();
     const int t = blockIdx.x;
@@ -116,7 +117,7 @@ talk_mix_kernel(const float* __restrict__ A, const void* __restrict__ talk, int 
         const int c = h / rep;
         float acc = 0.f;
         for (int g = 0; g < H; ++g)
-            acc = fmaf(bl_load_any(talk, talk_dtype, (size_t)h * H + g), A[(((size_t)t * H + g) * KV + c) * dv + d], acc);
+            acc = fmaf(bl_load_any(talk, talk_dtype, (size_t)h * H + g), bl_load(A + (((size_t)t * H + g) * KV + c) * dv + d), acc);
         bl_store(out + (size_t)t * H * dv + e, acc);
     }
 }
@@ -148,15 +149,17 @@ extern "C" int bl_attention_talk_plain(const void* q, const void* k_cache, const
     return 0;
 }
 
-extern "C" int bl_talk_mix(const float* A, const void* talk, int talk_dtype, void* out, int out_dtype, int T, int H, int KV, int dv,
-                           void* stream) {
+extern "C" int bl_talk_mix(const void* A, int a_dtype, const void* talk, int talk_dtype, void* out, int out_dtype, int T, int H, int KV,
+                           int dv, void* stream) {
     if (T <= 0) return 0;
     if (H <= 0 || KV <= 0 || H % KV != 0 || dv <= 0) BL_FAIL("bl_talk_mix: bad sizes H=%d KV=%d dv=%d", H, KV, dv);
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == BL_F32) BL_CUDA(bl_launch_dependent(talk_mix_kernel<float>, dim3(T), dim3(128), 0, s, A, talk, talk_dtype, (float*)out, H, KV, dv));
-    else if (out_dtype == BL_BF16)
-        BL_CUDA(bl_launch_dependent(talk_mix_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, s, A, talk, talk_dtype, (__nv_bfloat16*)out, H, KV, dv));
-    else BL_FAIL("bl_talk_mix: unknown output dtype %d", out_dtype);
+#define BL_GO(TA, TT) BL_CUDA(bl_launch_dependent(talk_mix_kernel<TA, TT>, dim3(T), dim3(128), 0, s, (const TA*)A, talk, talk_dtype, (TT*)out, H, KV, dv))
+    if (a_dtype == BL_F32 && out_dtype == BL_F32) BL_GO(float, float);
+    else if (a_dtype == BL_F32 && out_dtype == BL_BF16) BL_GO(float, __nv_bfloat16);
+    else if (a_dtype == BL_BF16 && out_dtype == BL_BF16) BL_GO(__nv_bfloat16, __nv_bfloat16);
+    else BL_FAIL("bl_talk_mix: unsupported dtypes %d -> %d", a_dtype, out_dtype);
+#undef BL_GO
     BL_CHECK_LAUNCH("bl_talk_mix");
     return 0;
 }

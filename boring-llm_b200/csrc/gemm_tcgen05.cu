@@ -55,7 +55,8 @@ constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >
 template <int EPI, typename TO, int STAGES>
 __global__ void __launch_bounds__(128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out, int M, int N, int K) {
+               const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out, int M, int N, int K,
+               const int* __restrict__ tile_expert, int expert_rows) {
     constexpr bool GLU = EPI == BL_EPI_SWIGLU;
     extern __shared__ unsigned char smem_raw[];
     if (threadIdx.x == 0) { tma_prefetch_map(&map_a); tma_prefetch_map(&map_b); }
@@ -79,17 +80,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     // W does not depend on the kernel before this one: the loader starts W for the first ring of k blocks before the
     // dependent-launch wait (the stage's barrier expects x and W together; x follows after the wait)
+    // Grouped: every tile of 128 rows has a matrix of its own, W[tile_expert[tile]] of a stack of matrices with
+    // `expert_rows` rows each (tile_expert null: one matrix for all rows; a negative entry: the tile has no rows).
+    int w_row0 = 0;
     auto load_w = [&](int s, int kb) {
         const uint32_t b_dst = base + s * STAGE_BYTES + A_BYTES;
         if (GLU) {                                                              // 64 gate rows, then the 64 up rows that match
-            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BK, n0);
-            tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * BK, N + n0);
+            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BK, w_row0 + n0);
+            tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * BK, w_row0 + N + n0);
         } else {
-            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BK, n0);
+            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BK, w_row0 + n0);
         }
     };
     int early = 0;
-    if (warp == 0 && lane == 0) {
+    if (tile_expert == nullptr && warp == 0 && lane == 0) {                     // (which matrix a grouped tile reads is the predecessor's result)
         for (; early < STAGES && early < kblocks; ++early) {
             mbar_expect_tx(full0 + 8 * early, STAGE_BYTES);
             load_w(early, early);
@@ -97,6 +101,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     __syncwarp();
     bl_pdl_wait();                                                              // x, out and the SM's tensor memory belong to the predecessor until here
+    if (tile_expert != nullptr) {
+        const int e = tile_expert[blockIdx.y];
+        if (e < 0) return;                                                      // the whole block: nothing allocated, no copy in flight
+        w_row0 = e * expert_rows;
+    }
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -231,7 +240,7 @@ int sm_count() {
 
 template <int EPI, typename TO, int STAGES>
 int launch_stages(const CUtensorMap& a, const CUtensorMap& b, const void* bias, int bias_dtype, void* out, int M, int N, int K,
-                  dim3 grid, cudaStream_t s) {
+                  dim3 grid, cudaStream_t s, const int* tile_expert = nullptr, int expert_rows = 0) {
     static bool configured = false;
     if (!configured) {
         BL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<EPI, TO, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(STAGES)));
@@ -239,19 +248,21 @@ int launch_stages(const CUtensorMap& a, const CUtensorMap& b, const void* bias, 
     }
     // a block waits (griddepcontrol.wait) before it allocates tensor memory or touches x and out, so it may be launched
     // while its predecessor still runs
-    BL_CUDA(bl_launch_dependent(gemm_tc_kernel<EPI, TO, STAGES>, grid, dim3(128), (size_t)smem_bytes(STAGES), s, a, b, bias, bias_dtype, (TO*)out, M, N, K));
+    BL_CUDA(bl_launch_dependent(gemm_tc_kernel<EPI, TO, STAGES>, grid, dim3(128), (size_t)smem_bytes(STAGES), s, a, b, bias, bias_dtype, (TO*)out, M, N, K,
+                                tile_expert, expert_rows));
     BL_CHECK_LAUNCH("bl_gemm_tc");
     return 0;
 }
 
 template <int EPI, typename TO>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const void* bias, int bias_dtype, void* out, int M, int N, int K,
-           cudaStream_t s) {
+           cudaStream_t s, const int* tile_expert = nullptr, int expert_rows = 0) {
     const int cols_per_tile = EPI == BL_EPI_SWIGLU ? BN / 2 : BN;
     dim3 grid((N + cols_per_tile - 1) / cols_per_tile, (M + BM - 1) / BM);
     // (the sums of a tile do not depend on the depth of the ring)
-    if ((long long)grid.x * grid.y <= sm_count()) return launch_stages<EPI, TO, STAGES_ALONE>(a, b, bias, bias_dtype, out, M, N, K, grid, s);
-    return launch_stages<EPI, TO, STAGES_SHARED>(a, b, bias, bias_dtype, out, M, N, K, grid, s);
+    if ((long long)grid.x * grid.y <= sm_count())
+        return launch_stages<EPI, TO, STAGES_ALONE>(a, b, bias, bias_dtype, out, M, N, K, grid, s, tile_expert, expert_rows);
+    return launch_stages<EPI, TO, STAGES_SHARED>(a, b, bias, bias_dtype, out, M, N, K, grid, s, tile_expert, expert_rows);
 }
 
 }  // namespace
@@ -288,6 +299,30 @@ extern "C" int bl_gemm_tc(const void* x, const void* w, const void* bias, int bi
         BL_FAIL("bl_gemm_tc: unknown output dtype %d", out_dtype);
     }
     BL_FAIL("bl_gemm_tc: unknown epilogue %d", epilogue);
+}
+
+// The grouped product: x [M, K] lies in tiles of 128 rows, tile i belonging to matrix tile_expert[i] (negative: the tile is
+// empty and skipped) of the stack w [n_experts, N, K] ([n_experts, 2N, K], gate rows then up rows, for BL_EPI_SWIGLU);
+// out [M, N] = epilogue(x . W[expert of the row's tile]^T). M a multiple of 128; epilogues BL_EPI_NONE and BL_EPI_SWIGLU.
+extern "C" int bl_gemm_tc_grouped(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int epilogue,
+                                  int n_experts, const int* tile_expert, void* stream) {
+    if (M <= 0) return 0;
+    if (N <= 0 || K <= 0 || n_experts <= 0 || M % BM != 0 || tile_expert == nullptr)
+        BL_FAIL("bl_gemm_tc_grouped: bad sizes M=%d N=%d K=%d experts=%d", M, N, K, n_experts);
+    if (K % 8 != 0) BL_FAIL("bl_gemm_tc_grouped: K=%d is not a multiple of 8 (TMA rows must be 16-byte multiples)", K);
+    if (((uintptr_t)x | (uintptr_t)w) & 15) BL_FAIL("bl_gemm_tc_grouped: x and W must be 16-byte aligned");
+    const bool glu = epilogue == BL_EPI_SWIGLU;
+    const int expert_rows = glu ? 2 * N : N;
+    if ((long long)n_experts * expert_rows > 0x7fffffffLL) BL_FAIL("bl_gemm_tc_grouped: the stack of matrices has too many rows");
+    CUtensorMap a, b;
+    if (bl_make_map_bf16("bl_gemm_tc_grouped", &a, x, M, K, BM, BK)) return 1;
+    if (bl_make_map_bf16("bl_gemm_tc_grouped", &b, w, n_experts * expert_rows, K, glu ? BN / 2 : BN, BK)) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == BL_F32 && epilogue == BL_EPI_NONE) return launch<BL_EPI_NONE, float>(a, b, nullptr, 0, out, M, N, K, s, tile_expert, expert_rows);
+    if (out_dtype == BL_BF16 && epilogue == BL_EPI_NONE) return launch<BL_EPI_NONE, __nv_bfloat16>(a, b, nullptr, 0, out, M, N, K, s, tile_expert, expert_rows);
+    if (out_dtype == BL_BF16 && glu) return launch<BL_EPI_SWIGLU, __nv_bfloat16>(a, b, nullptr, 0, out, M, N, K, s, tile_expert, expert_rows);
+    if (out_dtype == BL_F32 && glu) return launch<BL_EPI_SWIGLU, float>(a, b, nullptr, 0, out, M, N, K, s, tile_expert, expert_rows);
+    BL_FAIL("bl_gemm_tc_grouped: epilogue %d with output dtype %d is not built", epilogue, out_dtype);
 }
 
 // Reads and clears the status word: 0 when no block has given up on a wait since the last call

@@ -114,6 +114,65 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
     }
 }
 
+// The rows of a grouped product: pairs (token, chosen expert) laid out expert by expert in tiles of `tile` rows, every
+// expert's rows starting a new tile. One block. pos[p]: the row of pair p; row_src[row]: the pair of a row (-1: padding);
+// tile_expert[i]: the expert of tile i (-1: unused). Which of an expert's rows a pair gets depends on the order in which
+// the threads arrive; a row's result does not depend on where it lies.
+constexpr int PLAN_THREADS = 1024;
+__global__ void __launch_bounds__(PLAN_THREADS)
+moe_plan_kernel(const int* __restrict__ ids, int P, int E, int tile, int max_tiles, int* __restrict__ pos, int* __restrict__ row_src,
+                int* __restrict__ tile_expert) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    extern __shared__ int sh[];                        // counts [E], first tile [E + 1]
+    int* counts = sh;
+    int* first = sh + E;
+    for (int e = threadIdx.x; e < E; e += PLAN_THREADS) counts[e] = 0;
+    for (int i = threadIdx.x; i < max_tiles; i += PLAN_THREADS) tile_expert[i] = -1;
+    for (int i = threadIdx.x; i < max_tiles * tile; i += PLAN_THREADS) row_src[i] = -1;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += PLAN_THREADS) pos[p] = atomicAdd(&counts[ids[p]], 1);      // the pair's rank in its expert
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int e = 0; e < E; ++e) { first[e] = t; t += (counts[e] + tile - 1) / tile; }
+        first[E] = t;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += PLAN_THREADS)
+        for (int i = first[e]; i < first[e + 1]; ++i) tile_expert[i] = e;
+    for (int p = threadIdx.x; p < P; p += PLAN_THREADS) {
+        const int row = first[ids[p]] * tile + pos[p];
+        pos[p] = row;
+        row_src[row] = p;
+    }
+}
+
+// dst[row, :] = x[row_src[row] / div, :] (zeros where row_src is negative): the rows of a grouped product, 16 bytes a thread.
+__global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ row_src, int div, uint4* __restrict__ dst,
+                                   int rows, int vecs) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)rows * vecs; i += (size_t)gridDim.x * blockDim.x) {
+        const int row = (int)(i / vecs), v = (int)(i % vecs);
+        const int src = row_src[row];
+        dst[i] = src >= 0 ? x[(size_t)(src / div) * vecs + v] : make_uint4(0, 0, 0, 0);
+    }
+}
+
+// out[t, :] = (add ? out[t, :] : 0) + sum_k wts[t, k] * y[pos[t * top + k], :], k ascending.
+__global__ void moe_combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ wts, float* out,
+                                        int top, int d, size_t count, int add) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / d, c = e % d;
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc = fmaf(wts[t * top + k], y[(size_t)pos[t * top + k] * d + c], acc);
+        out[e] = add ? out[e] + acc : acc;
+    }
+}
+
 template <typename TX, typename TW, typename TO>
 int launch_expert(const void* x, int x_div, const void* w, size_t stride, const int* ids, void* out, int P, int N, int K, int epi,
                   cudaStream_t s) {
@@ -177,5 +236,41 @@ extern "C" int bl_moe_combine(const float* y, const float* wts, float* out, int 
     const int blocks = (int)((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
     BL_CUDA(bl_launch_dependent(moe_combine_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, y, wts, out, top, d, count, add));
     BL_CHECK_LAUNCH("bl_moe_combine");
+    return 0;
+}
+
+// Lays the pairs (token, chosen expert) out for the grouped product (see moe_plan_kernel). max_tiles >= ceil(P / tile) + E.
+extern "C" int bl_moe_plan(const int* ids, int P, int E, int tile, int max_tiles, int* pos, int* row_src, int* tile_expert, void* stream) {
+    if (P <= 0) return 0;
+    if (E <= 0 || tile <= 0 || max_tiles < (P + tile - 1) / tile + E) BL_FAIL("bl_moe_plan: %d pairs, %d experts, %d tiles of %d", P, E, max_tiles, tile);
+    const size_t smem = (size_t)(2 * E + 1) * sizeof(int);
+    if (smem > 48 * 1024) BL_FAIL("bl_moe_plan: %d experts are too many for shared memory", E);
+    BL_CUDA(bl_launch_dependent(moe_plan_kernel, dim3(1), dim3(PLAN_THREADS), smem, (cudaStream_t)stream, ids, P, E, tile, max_tiles, pos,
+                                row_src, tile_expert));
+    BL_CHECK_LAUNCH("bl_moe_plan");
+    return 0;
+}
+
+// dst[row, :] = x[row_src[row] / div, :], zeros where row_src[row] < 0; rows of `cols` bfloat16 values, cols a multiple of 8.
+extern "C" int bl_gather_rows(const void* x, const int* row_src, int div, void* dst, int rows, int cols, void* stream) {
+    if (rows <= 0) return 0;
+    if (cols <= 0 || cols % 8 != 0 || div <= 0 || (((uintptr_t)x | (uintptr_t)dst) & 15)) BL_FAIL("bl_gather_rows: rows of %d values", cols);
+    const int vecs = cols / 8;
+    const size_t n = (size_t)rows * vecs;
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    BL_CUDA(bl_launch_dependent(gather_rows_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (const uint4*)x, row_src, div,
+                                (uint4*)dst, rows, vecs));
+    BL_CHECK_LAUNCH("bl_gather_rows");
+    return 0;
+}
+
+extern "C" int bl_moe_combine_rows(const float* y, const int* pos, const float* wts, float* out, int T, int top, int d, int add,
+                                   void* stream) {
+    if (T <= 0) return 0;
+    if (top <= 0 || d <= 0) BL_FAIL("bl_moe_combine_rows: bad sizes top=%d d=%d", top, d);
+    const size_t count = (size_t)T * d;
+    const int blocks = (int)((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
+    BL_CUDA(bl_launch_dependent(moe_combine_rows_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, y, pos, wts, out, top, d, count, add));
+    BL_CHECK_LAUNCH("bl_moe_combine_rows");
     return 0;
 }

@@ -25,7 +25,7 @@ qk_norm_rope_write_kernel(const float* proj, int ld, int off_k, int off_v, const
                           const int* __restrict__ tok_req, const int* __restrict__ block_table, int max_pages,
                           const float* __restrict__ inv_freq, int rot_half, int pair_layout, TT* __restrict__ q_out,
                           TT* __restrict__ k_cache, TT* __restrict__ v_cache, int H, int KV, int dk, int dv, int page_size,
-                          int per_head) {
+                          int per_head, const float* __restrict__ q_head_scale) {
     bl_pdl_trigger();
     bl_pdl_wait();
     extern __shared__ float cs[];                      // cos [rot_half], sin [rot_half], then (per_head) 1 / rms of each of the H + KV heads
@@ -87,7 +87,7 @@ qk_norm_rope_write_kernel(const float* proj, int ld, int off_k, int off_v, const
             val = normed(d);
         }
         if (is_q) {
-            bl_store(q_out + (size_t)t * H * dk + e, val);
+            bl_store(q_out + (size_t)t * H * dk + e, q_head_scale ? val * q_head_scale[hh] : val);
         } else if (k_cache) {
             bl_store(k_cache + (((size_t)page * KV + (hh - H)) * page_size + in_page) * dk + d, val);
         }
@@ -109,14 +109,14 @@ extern "C" int bl_qk_norm_rope_write(const float* proj, int ld, int off_k, int o
                                      int KV, int dk, int dv, int page_size, void* stream) {
     return bl_qk_norm_rope_write_scope(proj, ld, off_k, off_v, q_norm_w, qw_dtype, k_norm_w, kw_dtype, eps, 0, positions, tok_req,
                                        block_table, max_pages, inv_freq, rot_half, pair_layout, q_out, k_cache, v_cache, dtype, T, H,
-                                       KV, dk, dv, page_size, stream);
+                                       KV, dk, dv, page_size, nullptr, stream);
 }
 
 extern "C" int bl_qk_norm_rope_write_scope(const float* proj, int ld, int off_k, int off_v, const void* q_norm_w, int qw_dtype,
                                            const void* k_norm_w, int kw_dtype, float eps, int per_head, const int* positions,
                                            const int* tok_req, const int* block_table, int max_pages, const float* inv_freq,
                                            int rot_half, int pair_layout, void* q_out, void* k_cache, void* v_cache, int dtype, int T,
-                                           int H, int KV, int dk, int dv, int page_size, void* stream) {
+                                           int H, int KV, int dk, int dv, int page_size, const float* q_head_scale, void* stream) {
     if (T <= 0) return 0;
     if (H <= 0 || KV <= 0 || dk <= 0 || dv <= 0 || rot_half < 0 || 2 * rot_half > dk || page_size <= 0)
         BL_FAIL("bl_qk_norm_rope_write: bad sizes H=%d KV=%d dk=%d dv=%d rotated pairs=%d page=%d", H, KV, dk, dv, rot_half, page_size);
@@ -126,7 +126,7 @@ extern "C" int bl_qk_norm_rope_write_scope(const float* proj, int ld, int off_k,
     const size_t smem = (size_t)(2 * rot_half + 1 + (per_head ? H + KV : 0)) * sizeof(float);
 #define BL_GO(TT) BL_CUDA(bl_launch_dependent(qk_norm_rope_write_kernel<TT>, dim3(T), dim3(THREADS), smem, s, proj, ld, off_k, off_v, \
         q_norm_w, qw_dtype, k_norm_w, kw_dtype, eps, positions, tok_req, block_table, max_pages, inv_freq, rot_half, pair_layout, \
-        (TT*)q_out, (TT*)k_cache, (TT*)v_cache, H, KV, dk, dv, page_size, per_head))
+        (TT*)q_out, (TT*)k_cache, (TT*)v_cache, H, KV, dk, dv, page_size, per_head, q_head_scale))
     if (dtype == BL_F32) BL_GO(float);
     else if (dtype == BL_BF16) BL_GO(__nv_bfloat16);
     else BL_FAIL("bl_qk_norm_rope_write: unknown dtype %d", dtype);

@@ -443,20 +443,22 @@ __global__ void scan_fold_kernel(float* state, size_t slot_stride, const int* __
     S[e] = sv;
 }
 
-// y[t, h, :] = u / sqrt(mean(u^2) + eps) * w * gate(g[t, h, :]), u = o[t, h, :] / den[t, h] (den null: u = o); w is one
-// vector of dv values shared by the heads, or (w_per_head) H * dv values; one warp per (token, head).
+// y[t, h, :] = u / sqrt(mean(u^2) + eps) * w * gate(g[t, h, :]); w is one vector of dv values shared by the heads, or
+// (w_per_head) H * dv values. The heads of a row of o lie o_head_stride values apart. floor null: u = o[t, h, :dv]; else
+// u = o[t, h, :dv] / (max(|o[t, h, dv]|, floor[t, h]) + 1e-6): the read-out of a matrix memory whose normaliser was walked
+// as one more value column. One warp per (token, head).
 template <typename TY>
 __global__ void __launch_bounds__(WARPS * 32)
-head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, int w_per_head, const float* den, const float* gate,
-                      int ld_gate, int gate_kind, TY* __restrict__ y, int items, int H, int dv, float eps) {
+head_norm_gate_kernel(const float* o, int o_head_stride, const void* __restrict__ w, int w_dtype, int w_per_head, const float* floor,
+                      const float* gate, int ld_gate, int gate_kind, TY* __restrict__ y, int items, int H, int dv, float eps) {
     bl_pdl_trigger();
     bl_pdl_wait();
     const int lane = threadIdx.x & 31;
     const int item = blockIdx.x * WARPS + (threadIdx.x >> 5);
     if (item >= items) return;
     const int t = item / H, h = item % H;
-    const float* src = o + (size_t)item * dv;
-    const float pre = den ? 1.0f / den[item] : 1.0f;
+    const float* src = o + (size_t)item * o_head_stride;
+    const float pre = floor ? 1.0f / (fmaxf(fabsf(src[dv]), floor[item]) + 1e-6f) : 1.0f;
     float ss = 0.f;
     for (int i = lane; i < dv; i += 32) { const float u = src[i] * pre; ss += u * u; }
     const float inv = pre / sqrtf(bl_warp_sum(ss) / (float)dv + eps);
@@ -469,41 +471,34 @@ head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, i
     }
 }
 
-// The gates of a matrix memory with exponential gating, one warp per (request, head), the request's tokens in order.
+// The gates of a matrix memory with exponential gating: one warp per (request, head) walks the request's tokens in order.
 // Per token: log input gate i = cap tanh((zi + bi) / cap), log forget gate f = log sigmoid(cap tanh((zf + bf) / cap)), the
-// running maximum m' = max(f + m, i) (m starts at 0 in a fresh slot), decay a = e^(f + m - m'), input weight e = e^(i - m');
-// the normaliser n' = a n + e k per key channel, and den = max(|n' . q| q_scale, e^(-m')) + 1e-6. Out: the decay for every
-// key channel of the head (what the scan reads), e k, den. n [H, dk] and m [H] live in the slot at off_n and off_m.
-// Tokens are taken 32 at a time: the gates of 32 tokens in parallel (a lane each), the maxima as a chain of 32 steps of
-// two instructions, then the normaliser token by token with the lanes over the key channels.
-constexpr int GATE_MAX_ROWS = 16;                      // key channels a lane holds (dk <= 512)
+// running maximum m' = max(f + m, i) (m starts at 0 in a fresh slot and is kept in the slot at off_m), and from them the
+// decay a = e^(f + m - m'), the input weight e = e^(i - m') and the floor e^(-m') of the read-out's denominator, into
+// gates [3, T, H]. 32 tokens at a time: their gates in parallel (a lane each; the next 32 tokens' pre-activations are
+// fetched before), the maxima as a chain of 32 steps of two dependent instructions.
 __global__ void __launch_bounds__(32)
-memory_gates_kernel(const float* proj, int ld, int off_q, int off_k, int off_i, int off_f, const void* __restrict__ bi, int bi_dtype,
-                    const void* __restrict__ bf, int bf_dtype, float cap, float q_scale, float* state, size_t slot_stride,
-                    size_t off_n, size_t off_m, const int* __restrict__ slots, const int* __restrict__ cu_q,
-                    float* a_out, float* k_out, float* den_out, int H, int dk) {
+memory_gate_chain_kernel(const float* proj, int ld, int off_i, int off_f, const void* __restrict__ bi, int bi_dtype,
+                         const void* __restrict__ bf, int bf_dtype, float cap, float* state, size_t slot_stride, size_t off_m,
+                         const int* __restrict__ slots, const int* __restrict__ cu_q, float* gates, int T, int H) {
     bl_pdl_trigger();
     bl_pdl_wait();
     const int r = blockIdx.y, h = blockIdx.x, lane = threadIdx.x;
     const int t0 = cu_q[r], n_tok = cu_q[r + 1] - t0;
     if (n_tok <= 0) return;
-    float* slot = state + (size_t)slots[r] * slot_stride;
-    float* np = slot + off_n + (size_t)h * dk;
-    float nreg[GATE_MAX_ROWS];
-#pragma unroll
-    for (int j = 0; j < GATE_MAX_ROWS; ++j) nreg[j] = lane + 32 * j < dk ? np[lane + 32 * j] : 0.f;
-    float m = slot[off_m + h];
+    float* mp = state + (size_t)slots[r] * slot_stride + off_m + h;
+    float m = *mp;
     const float b_i = bl_load_any(bi, bi_dtype, h), b_f = bl_load_any(bf, bf_dtype, h);
     const float inv_cap = 1.0f / cap;
+    float zi = 0.f, zf = 0.f;
+    if (lane < n_tok) { const float* row = proj + (size_t)(t0 + lane) * ld; zi = row[off_i + h]; zf = row[off_f + h]; }
     for (int base = 0; base < n_tok; base += 32) {
         const int cnt = min(32, n_tok - base);
-        float gi = 0.f, gf = 0.f;
-        if (lane < cnt) {
-            const float* row = proj + (size_t)(t0 + base + lane) * ld;
-            gi = cap * tanhf((row[off_i + h] + b_i) * inv_cap);
-            const float z = cap * tanhf((row[off_f + h] + b_f) * inv_cap);
-            gf = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-        }
+        float nzi = 0.f, nzf = 0.f;
+        if (base + 32 + lane < n_tok) { const float* row = proj + (size_t)(t0 + base + 32 + lane) * ld; nzi = row[off_i + h]; nzf = row[off_f + h]; }
+        const float gi = cap * tanhf((zi + b_i) * inv_cap);
+        const float z = cap * tanhf((zf + b_f) * inv_cap);
+        const float gf = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
         float m_before = 0.f, m_mine = 0.f;
         for (int tt = 0; tt < cnt; ++tt) {
             const float f_t = __shfl_sync(0xffffffffu, gf, tt), i_t = __shfl_sync(0xffffffffu, gi, tt);
@@ -511,33 +506,36 @@ memory_gates_kernel(const float* proj, int ld, int off_q, int off_k, int off_i, 
             if (lane == tt) { m_before = m; m_mine = m_new; }
             m = m_new;
         }
-        const float a_mine = expf(gf + m_before - m_mine), e_mine = expf(gi - m_mine), floor_mine = expf(-m_mine);
-        float den_mine = 0.f;
-        for (int tt = 0; tt < cnt; ++tt) {
-            const float a = __shfl_sync(0xffffffffu, a_mine, tt), e = __shfl_sync(0xffffffffu, e_mine, tt);
-            const size_t tok = (size_t)(t0 + base + tt);
-            const float* qr = proj + tok * ld + off_q + (size_t)h * dk;
-            const float* kr = proj + tok * ld + off_k + (size_t)h * dk;
-            float dot = 0.f;
-#pragma unroll
-            for (int j = 0; j < GATE_MAX_ROWS; ++j) {
-                const int c = lane + 32 * j;
-                if (c < dk) {
-                    const float ek = e * kr[c];
-                    nreg[j] = fmaf(a, nreg[j], ek);
-                    dot = fmaf(nreg[j], qr[c], dot);
-                    a_out[tok * H * dk + (size_t)h * dk + c] = a;
-                    k_out[tok * H * dk + (size_t)h * dk + c] = ek;
-                }
-            }
-            dot = bl_warp_sum(dot) * q_scale;
-            if (lane == tt) den_mine = fmaxf(fabsf(dot), floor_mine) + 1e-6f;
+        if (lane < cnt) {
+            const size_t at = (size_t)(t0 + base + lane) * H + h;
+            gates[at] = expf(gf + m_before - m_mine);
+            gates[(size_t)T * H + at] = expf(gi - m_mine);
+            gates[2 * (size_t)T * H + at] = expf(-m_mine);
         }
-        if (lane < cnt) den_out[(size_t)(t0 + base + lane) * H + h] = den_mine;
+        zi = nzi; zf = nzf;
     }
-#pragma unroll
-    for (int j = 0; j < GATE_MAX_ROWS; ++j) if (lane + 32 * j < dk) np[lane + 32 * j] = nreg[j];
-    if (lane == 0) slot[off_m + h] = m;
+    if (lane == 0) *mp = m;
+}
+
+// What the scan of a matrix memory reads, from the projections and the gates: decay[t, h, :] = a[t, h] for every key
+// channel, k_out[t, h, :] = e[t, h] * k[t, h, :], v_out[t, h, :] = (v[t, h, :], 1): the one in the last column makes the
+// normaliser n the state's last value column, and n . q the last column of the read-out. One block per token.
+__global__ void __launch_bounds__(WARPS * 32)
+memory_expand_kernel(const float* proj, int ld, int off_k, int off_v, const float* __restrict__ gates, float* decay, float* k_out,
+                     float* v_out, int T, int H, int dk, int dv) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int t = blockIdx.x;
+    const float* row = proj + (size_t)t * ld;
+    for (int e = threadIdx.x; e < H * dk; e += WARPS * 32) {
+        const size_t g = (size_t)t * H + e / dk;
+        decay[(size_t)t * H * dk + e] = gates[g];
+        k_out[(size_t)t * H * dk + e] = gates[(size_t)T * H + g] * row[off_k + e];
+    }
+    for (int e = threadIdx.x; e < H * (dv + 1); e += WARPS * 32) {
+        const int h = e / (dv + 1), c = e % (dv + 1);
+        v_out[(size_t)t * H * (dv + 1) + e] = c < dv ? row[off_v + h * dv + c] : 1.0f;
+    }
 }
 
 // Token shift: out[s, t, c] = x[t, c] + (x'[t, c] - x[t, c]) * mu[s, c] for s < n_mix, x' the row of the request's token
@@ -744,39 +742,43 @@ extern "C" int bl_recurrent_scan_parts(int rule, const float* q, int ldq, const 
 
 extern "C" int bl_head_norm_gate(const float* o, const void* w, int w_dtype, const float* gate, int ld_gate, int gate_kind,
                                  void* y, int y_dtype, int T, int H, int dv, float eps, void* stream) {
-    return bl_head_norm_gate_ext(o, w, w_dtype, 0, nullptr, gate, ld_gate, gate_kind, y, y_dtype, T, H, dv, eps, stream);
+    return bl_head_norm_gate_ext(o, dv, w, w_dtype, 0, nullptr, gate, ld_gate, gate_kind, y, y_dtype, T, H, dv, eps, stream);
 }
 
-extern "C" int bl_head_norm_gate_ext(const float* o, const void* w, int w_dtype, int w_per_head, const float* den, const float* gate,
-                                     int ld_gate, int gate_kind, void* y, int y_dtype, int T, int H, int dv, float eps, void* stream) {
+extern "C" int bl_head_norm_gate_ext(const float* o, int o_head_stride, const void* w, int w_dtype, int w_per_head, const float* floor,
+                                     const float* gate, int ld_gate, int gate_kind, void* y, int y_dtype, int T, int H, int dv, float eps,
+                                     void* stream) {
     if (T <= 0) return 0;
-    if (H <= 0 || dv <= 0 || (gate && ld_gate < H * dv)) BL_FAIL("bl_head_norm_gate: bad sizes H=%d dv=%d gate stride %d", H, dv, ld_gate);
+    if (H <= 0 || dv <= 0 || (gate && ld_gate < H * dv) || o_head_stride < dv + (floor ? 1 : 0))
+        BL_FAIL("bl_head_norm_gate: bad sizes H=%d dv=%d gate stride %d head stride %d", H, dv, ld_gate, o_head_stride);
     if (gate && gate_kind != BL_GATE_SIGMOID && gate_kind != BL_GATE_SILU) BL_FAIL("bl_head_norm_gate: unknown gate %d", gate_kind);
     const int items = T * H, blocks = (items + WARPS - 1) / WARPS;
     cudaStream_t s = (cudaStream_t)stream;
     if (y_dtype == BL_F32)
-        BL_CUDA(bl_launch_dependent(head_norm_gate_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, s, o, w, w_dtype, w_per_head, den, gate,
-                                    ld_gate, gate_kind, (float*)y, items, H, dv, eps));
+        BL_CUDA(bl_launch_dependent(head_norm_gate_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, s, o, o_head_stride, w, w_dtype, w_per_head,
+                                    floor, gate, ld_gate, gate_kind, (float*)y, items, H, dv, eps));
     else if (y_dtype == BL_BF16)
-        BL_CUDA(bl_launch_dependent(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, s, o, w, w_dtype, w_per_head, den,
-                                    gate, ld_gate, gate_kind, (__nv_bfloat16*)y, items, H, dv, eps));
+        BL_CUDA(bl_launch_dependent(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, s, o, o_head_stride, w, w_dtype,
+                                    w_per_head, floor, gate, ld_gate, gate_kind, (__nv_bfloat16*)y, items, H, dv, eps));
     else
         BL_FAIL("bl_head_norm_gate: unknown output dtype %d", y_dtype);
     BL_CHECK_LAUNCH("bl_head_norm_gate");
     return 0;
 }
 
-extern "C" int bl_memory_gates(const float* proj, int ld, int off_q, int off_k, int off_i, int off_f, const void* bias_i, int bi_dtype,
-                               const void* bias_f, int bf_dtype, float cap, float q_scale, float* state, long long slot_stride,
-                               long long off_n, long long off_m, const int* slots, const int* cu_q, int R, float* a_out, float* k_out,
-                               float* den_out, int H, int dk, void* stream) {
-    if (R <= 0) return 0;
-    if (H <= 0 || dk <= 0 || dk > GATE_MAX_ROWS * 32 || !(cap > 0.f)) BL_FAIL("bl_memory_gates: bad sizes H=%d dk=%d cap=%g", H, dk, cap);
+extern "C" int bl_memory_gates(const float* proj, int ld, int off_k, int off_v, int off_i, int off_f, const void* bias_i, int bi_dtype,
+                               const void* bias_f, int bf_dtype, float cap, float* state, long long slot_stride, long long off_m,
+                               const int* slots, const int* cu_q, int R, int T, float* gates, float* decay, float* k_out, float* v_out,
+                               int H, int dk, int dv, void* stream) {
+    if (R <= 0 || T <= 0) return 0;
+    if (H <= 0 || dk <= 0 || dv <= 0 || !(cap > 0.f)) BL_FAIL("bl_memory_gates: bad sizes H=%d dk=%d dv=%d cap=%g", H, dk, dv, cap);
     if (R > 65535) BL_FAIL("bl_memory_gates: %d requests are too many for one launch", R);
-    if (off_q + H * dk > ld || off_k + H * dk > ld || off_i + H > ld || off_f + H > ld) BL_FAIL("bl_memory_gates: columns do not fit rows of %d", ld);
-    BL_CUDA(bl_launch_dependent(memory_gates_kernel, dim3(H, R), dim3(32), 0, (cudaStream_t)stream, proj, ld, off_q, off_k, off_i, off_f,
-                                bias_i, bi_dtype, bias_f, bf_dtype, cap, q_scale, state, (size_t)slot_stride, (size_t)off_n, (size_t)off_m,
-                                slots, cu_q, a_out, k_out, den_out, H, dk));
+    if (off_k + H * dk > ld || off_v + H * dv > ld || off_i + H > ld || off_f + H > ld) BL_FAIL("bl_memory_gates: columns do not fit rows of %d", ld);
+    cudaStream_t s = (cudaStream_t)stream;
+    BL_CUDA(bl_launch_dependent(memory_gate_chain_kernel, dim3(H, R), dim3(32), 0, s, proj, ld, off_i, off_f, bias_i, bi_dtype, bias_f, bf_dtype,
+                                cap, state, (size_t)slot_stride, (size_t)off_m, slots, cu_q, gates, T, H));
+    BL_CUDA(bl_launch_dependent(memory_expand_kernel, dim3(T), dim3(WARPS * 32), 0, s, proj, ld, off_k, off_v, (const float*)gates, decay, k_out,
+                                v_out, T, H, dk, dv));
     BL_CHECK_LAUNCH("bl_memory_gates");
     return 0;
 }

@@ -1087,8 +1087,10 @@ def pair_rms_mean(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.
 def qk_head_norm_rope_write(proj: torch.Tensor, off_k: int, off_v: int, q_norm_w: Optional[torch.Tensor],
                             k_norm_w: Optional[torch.Tensor], eps: float, positions: torch.Tensor, tok_req: torch.Tensor,
                             block_table: torch.Tensor, inv_freq: torch.Tensor, rot_half: int, pair_layout: int, q_out: torch.Tensor,
-                            k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], H: int, KV: int, dk: int, dv: int) -> None:
-    """`qk_norm_rope_write` with an RMS norm over each HEAD of q and of k (weights [dk], shared by the heads)."""
+                            k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], H: int, KV: int, dk: int, dv: int,
+                            q_head_scale: Optional[torch.Tensor] = None) -> None:
+    """`qk_norm_rope_write` with an RMS norm over each HEAD of q and of k (weights [dk], shared by the heads), and an optional
+    factor per head on q (32-bit [H]), applied as q is written."""
     T = proj.shape[0]
     ld = _rows32(proj, "proj", T, off_v + KV * dv)
     _need(positions, "positions", torch.int32, (T,)); _need(tok_req, "tok_req", torch.int32, (T,))
@@ -1099,6 +1101,8 @@ def qk_head_norm_rope_write(proj: torch.Tensor, off_k: int, off_v: int, q_norm_w
     for w, name in ((q_norm_w, "q_norm_w"), (k_norm_w, "k_norm_w")):
         if w is not None:
             _need(w, name, None, (dk,))
+    if q_head_scale is not None:
+        _need(q_head_scale, "q_head_scale", torch.float32, (H,))
     page_size = 1
     if k_cache is not None:
         _need(k_cache, "k_cache", q_out.dtype); _need(v_cache, "v_cache", q_out.dtype)
@@ -1107,7 +1111,8 @@ def qk_head_norm_rope_write(proj: torch.Tensor, off_k: int, off_v: int, q_norm_w
         page_size = k_cache.shape[2]
     _call(_lib().bl_qk_norm_rope_write_scope, _p(proj), ld, off_k, off_v, _p(q_norm_w), _vec_dt(q_norm_w), _p(k_norm_w),
           _vec_dt(k_norm_w), ctypes.c_float(eps), 1, _p(positions), _p(tok_req), _p(block_table), block_table.shape[1],
-          _p(inv_freq), rot_half, pair_layout, _p(q_out), _p(k_cache), _p(v_cache), _dt(q_out), T, H, KV, dk, dv, page_size, _stream())
+          _p(inv_freq), rot_half, pair_layout, _p(q_out), _p(k_cache), _p(v_cache), _dt(q_out), T, H, KV, dk, dv, page_size,
+          _p(q_head_scale), _stream())
 
 
 def attention_talk_plain(q, k_cache, v_cache, tok_req, cu_q, ctx_len, block_table, A: torch.Tensor, H: int, chunk: int, window: int,
@@ -1130,8 +1135,32 @@ def attention_talk_plain(q, k_cache, v_cache, tok_req, cu_q, ctx_len, block_tabl
 def talk_mix(A: torch.Tensor, talk: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, h] = sum_g talk[h, g] * A[t, g, kv(h)]: the heads' softmax weights mixed, applied to each head's own values."""
     T, H, KV, dv = A.shape
-    _need(A, "A", torch.float32); _need(talk, "talk", None, (H, H)); _need(out, "out", None, (T, H * dv))
-    _call(_lib().bl_talk_mix, _p(A), _p(talk), _dt(talk), _p(out), _dt(out), T, H, KV, dv, _stream())
+    _need(A, "A"); _need(talk, "talk", None, (H, H)); _need(out, "out", None, (T, H * dv))
+    _call(_lib().bl_talk_mix, _p(A), _dt(A), _p(talk), _dt(talk), _p(out), _dt(out), T, H, KV, dv, _stream())
+
+
+def attention_prefill_talk(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles, A: torch.Tensor, H: int, chunk: int, window: int,
+                           scale: float, head_scale: Optional[torch.Tensor]) -> None:
+    """`attention_talk_plain` on tensor cores for the requests with several new tokens (tiles as `attention_prefill`);
+    A: bfloat16 [T, H, KV, dh]; head_scale 32-bit and positive."""
+    KV, dh = k_cache.shape[1], k_cache.shape[3]
+    _need(q, "q", torch.bfloat16); _need(A, "A", torch.bfloat16, (q.shape[0], H, KV, dh)); _need(tiles, "tiles", torch.int32)
+    if head_scale is not None:
+        _need(head_scale, "head_scale", torch.float32, (H,))
+    _call(_lib().bl_attention_prefill_talk, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table), block_table.shape[1],
+          _p(tiles), tiles.shape[0], _p(A), H, KV, dh, k_cache.shape[2], chunk, window, ctypes.c_float(scale), _p(head_scale), _stream())
+
+
+def attention_decode_talk(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_splits: int, A: torch.Tensor, H: int, chunk: int,
+                          window: int, scale: float, head_scale: Optional[torch.Tensor]) -> None:
+    """The same for the requests with a single new token (reqs, slices as `attention_decode` without scratch)."""
+    KV, dh = k_cache.shape[1], k_cache.shape[3]
+    _need(q, "q", torch.bfloat16); _need(A, "A", torch.bfloat16, (q.shape[0], H, KV, dh)); _need(reqs, "reqs", torch.int32)
+    if head_scale is not None:
+        _need(head_scale, "head_scale", torch.float32, (H,))
+    _call(_lib().bl_attention_decode_talk, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table), block_table.shape[1],
+          _p(reqs), reqs.shape[0], n_splits, _p(A), H, KV, dh, k_cache.shape[2], chunk, window, ctypes.c_float(scale), _p(head_scale),
+          _stream())
 
 
 def gemm_plain_decay_exp(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, x_tanh: bool = False) -> None:
@@ -1151,36 +1180,39 @@ def _slot_rows(state: torch.Tensor, name: str, min_cols: int) -> None:
         raise KernelError(f"{name}: must be 32-bit [slots, >= {min_cols}] with contiguous rows")
 
 
-def memory_gates(proj: torch.Tensor, off_q: int, off_k: int, off_i: int, off_f: int, bias_i: torch.Tensor, bias_f: torch.Tensor,
-                 cap: float, q_scale: float, state: torch.Tensor, off_n: int, off_m: int, slots: torch.Tensor, cu_q: torch.Tensor,
-                 decay: torch.Tensor, k_out: torch.Tensor, den: torch.Tensor, H: int, dk: int) -> None:
+def memory_gates(proj: torch.Tensor, off_k: int, off_v: int, off_i: int, off_f: int, bias_i: torch.Tensor, bias_f: torch.Tensor,
+                 cap: float, state: torch.Tensor, off_m: int, slots: torch.Tensor, cu_q: torch.Tensor, H: int, dk: int, dv: int):
     """The gates of a matrix memory with exponential gating held against a running maximum (see `bl_memory_gates`): from
-    the joined projections, per token and head, the decay (written for every key channel: what `recurrent_scan` reads),
-    the keys times their input weight, and the read-out's denominator; the normaliser [H, dk] and the maximum [H] are kept
-    in the request's slot at `off_n` and `off_m`."""
+    the joined projections, what the scan reads, (decay [T, H * dk], keys times their input weight [T, H * dk], values with
+    a last column of ones [T, H * (dv + 1)]), and the floor e^(-m) of the read-out's denominator [T, H]. The running maximum
+    [H] is kept in the request's slot at `off_m`; the normaliser is the state's last value column."""
     T = proj.shape[0]
     ld = _rows32(proj, "proj", T, 1)
-    _slot_rows(state, "state", max(off_n + H * dk, off_m + H))
-    _need(decay, "decay", torch.float32, (T, H * dk)); _need(k_out, "k_out", torch.float32, (T, H * dk)); _need(den, "den", torch.float32, (T, H))
+    _slot_rows(state, "state", off_m + H)
     _need(bias_i, "bias_i", None, (H,)); _need(bias_f, "bias_f", None, (H,))
     _need(slots, "slots", torch.int32); _need(cu_q, "cu_q", torch.int32)
-    _call(_lib().bl_memory_gates, _p(proj), ld, off_q, off_k, off_i, off_f, _p(bias_i), _dt(bias_i), _p(bias_f), _dt(bias_f),
-          ctypes.c_float(cap), ctypes.c_float(q_scale), _p(state), ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(off_n),
-          ctypes.c_longlong(off_m), _p(slots), _p(cu_q), cu_q.shape[0] - 1, _p(decay), _p(k_out), _p(den), H, dk, _stream())
+    f32 = dict(dtype=torch.float32, device=proj.device)
+    gates = torch.empty((3, T, H), **f32)
+    decay, keys, values = torch.empty((T, H * dk), **f32), torch.empty((T, H * dk), **f32), torch.empty((T, H * (dv + 1)), **f32)
+    _call(_lib().bl_memory_gates, _p(proj), ld, off_k, off_v, off_i, off_f, _p(bias_i), _dt(bias_i), _p(bias_f), _dt(bias_f),
+          ctypes.c_float(cap), _p(state), ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(off_m), _p(slots), _p(cu_q),
+          cu_q.shape[0] - 1, T, _p(gates), _p(decay), _p(keys), _p(values), H, dk, dv, _stream())
+    return decay, keys, values, gates[2]
 
 
 def head_norm_gate_ext(o: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], gate_kind: int, eps: float,
-                       out: torch.Tensor, H: int, dv: int, den: Optional[torch.Tensor] = None) -> None:
-    """`head_norm_gate` with a weight per head and channel when `weight` has H * dv values, and an optional divisor
-    den [T, H] applied to o before the norm."""
+                       out: torch.Tensor, H: int, dv: int, floor: Optional[torch.Tensor] = None) -> None:
+    """`head_norm_gate` with a weight per head and channel when `weight` has H * dv values; with `floor` [T, H], o has
+    dv + 1 columns a head, and o[t, h, :dv] is divided by max(|o[t, h, dv]|, floor[t, h]) + 1e-6 before the norm."""
     T = o.shape[0]
-    _need(o, "o", torch.float32, (T, H * dv)); _need(out, "out", None, (T, H * dv))
+    stride = dv + 1 if floor is not None else dv
+    _need(o, "o", torch.float32, (T, H * stride)); _need(out, "out", None, (T, H * dv))
     per_head = weight.numel() == H * dv and H > 1
     _need(weight, "weight", None, (H * dv,) if per_head else (dv,))
-    if den is not None:
-        _need(den, "den", torch.float32, (T, H))
+    if floor is not None:
+        _need(floor, "floor", torch.float32, (T, H))
     ld = _rows32(gate, "gate", T, H * dv) if gate is not None else 0
-    _call(_lib().bl_head_norm_gate_ext, _p(o), _p(weight), _dt(weight), 1 if per_head else 0, _p(den), _p(gate), ld, gate_kind,
+    _call(_lib().bl_head_norm_gate_ext, _p(o), stride, _p(weight), _dt(weight), 1 if per_head else 0, _p(floor), _p(gate), ld, gate_kind,
           _p(out), _dt(out), T, H, dv, ctypes.c_float(eps), _stream())
 
 
@@ -1235,3 +1267,53 @@ def moe_combine(y: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, add: bool
     d = out.shape[1]
     _need(y, "y", torch.float32, (T * top, d)); _need(wts, "wts", torch.float32); _need(out, "out", torch.float32, (T, d))
     _call(_lib().bl_moe_combine, _p(y), _p(wts), _p(out), T, top, d, 1 if add else 0, _stream())
+
+
+GROUPED_TILE = 128         # rows of a tile of the grouped tensor-core product (every expert's rows start a new tile)
+
+
+def grouped_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether `moe_grouped` takes these operands: bfloat16, inner sizes that are multiples of 8, 16-byte alignment."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.shape[2] % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def moe_plan(ids: torch.Tensor, n_experts: int):
+    """The layout of the pairs (token, chosen expert) for the grouped product: (pos [P] the row of each pair, row_src
+    [rows] the pair of each row or -1, tile_expert [tiles] the expert of each tile of 128 rows or -1). The number of
+    rows depends on the number of pairs and experts only (every expert may leave one tile partly empty)."""
+    P = ids.numel()
+    tiles = -(-P // GROUPED_TILE) + n_experts
+    _need(ids, "ids", torch.int32)
+    pos = torch.empty(P, dtype=torch.int32, device=ids.device)
+    row_src = torch.empty(tiles * GROUPED_TILE, dtype=torch.int32, device=ids.device)
+    tile_expert = torch.empty(tiles, dtype=torch.int32, device=ids.device)
+    _call(_lib().bl_moe_plan, _p(ids), P, n_experts, GROUPED_TILE, tiles, _p(pos), _p(row_src), _p(tile_expert), _stream())
+    return pos, row_src, tile_expert
+
+
+def gather_rows(x: torch.Tensor, row_src: torch.Tensor, div: int, out: torch.Tensor) -> None:
+    """out[row] = x[row_src[row] // div] (zeros where row_src is negative); bfloat16 rows of a multiple of 8 values."""
+    _need(x, "x", torch.bfloat16); _need(out, "out", torch.bfloat16, (row_src.numel(), x.shape[1])); _need(row_src, "row_src", torch.int32)
+    _call(_lib().bl_gather_rows, _p(x), _p(row_src), div, _p(out), out.shape[0], x.shape[1], _stream())
+
+
+def gemm_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE) -> None:
+    """out = epilogue(x @ w[expert of the row's tile].T) on tcgen05: x [tiles * 128, K] bfloat16 in tiles of 128 rows, w
+    [E, N, K] ([E, 2N, K], gate rows then up rows, for EPI_SWIGLU), tile_expert [tiles] (negative: an empty tile)."""
+    M, K = x.shape
+    N = out.shape[1]
+    E = w.shape[0]
+    _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (E, 2 * N if epilogue == EPI_SWIGLU else N, K))
+    _need(out, "out", None, (M, N)); _need(tile_expert, "tile_expert", torch.int32, (M // GROUPED_TILE,))
+    _call(_lib().bl_gemm_tc_grouped, _p(x), _p(w), _p(out), _dt(out), M, N, K, epilogue, E, _p(tile_expert), _stream())
+
+
+def moe_combine_rows(y: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, add: bool = False) -> None:
+    """out[t] = sum_k wts[t, k] * y[pos[t * top + k]], k ascending (32-bit); with `add` the sum is added to out."""
+    T, top = wts.shape
+    d = out.shape[1]
+    _need(y, "y", torch.float32); _need(pos, "pos", torch.int32, (T * top,)); _need(wts, "wts", torch.float32); _need(out, "out", torch.float32, (T, d))
+    if y.shape[1] != d:
+        raise KernelError("moe_combine_rows: y and out differ in width")
+    _call(_lib().bl_moe_combine_rows, _p(y), _p(pos), _p(wts), _p(out), T, top, d, 1 if add else 0, _stream())

@@ -368,7 +368,8 @@ class ChunkedTalkingAttention(Mixer):
 
     * q and k get an RMS norm per head (`qk_norm_eps`; weights of the head size, shared by the heads) before the rotation;
     * `rotary`: any `RotaryTable` (partial rotation, pairs in halves or interleaved);
-    * score = q . k * scale * temp[head], `temp` a learned number per head;
+    * score = q . k * scale * temp[head], `temp` a learned number per head (of either sign: it is multiplied into q as q is
+      written, in 32-bit);
     * `chunk` n > 0: position i sees j <= i with floor(i / n) = floor(j / n), chunks counted from position 0 of the
       sequence (0: every j <= i); `window` as in `GQAAttention`, on top of it;
     * softmax per head over the visible keys; then W'_h = sum_g talk[h, g] W_g (`talk` [H, H]), and head h applies W'_h to
@@ -413,6 +414,44 @@ class ChunkedTalkingAttention(Mixer):
     def cache_spec(self):
         return PagedKVSpec(self.KV, self.dk, self.window, 0 if self.dv == self.dk else self.dv, self.chunk)
 
+    def plan_step(self, q_lens, ctx_lens, filler=None):
+        return PLAN_KEY, attention_plan(q_lens, ctx_lens, filler)
+
+    def attend(self, ctx, q, k_cache, v_cache, table, attn):
+        """Every head's softmax over its chunk applied to the values of every key/value head, then the mix of the heads."""
+        T = q.shape[0]
+        # (the heads' factors on the scores are in q already; the tensor-core kernels want a positive scale)
+        fast = (ctx.fast and self.dv == self.dk and self.scale > 0
+                and ops.attention_mma_supported(q.dtype, self.dk, k_cache.shape[2]))
+        if not fast:
+            spread = ctx.empty((T, self.H, self.KV, self.dv), torch.float32)
+            ops.attention_talk_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, spread, self.H, self.chunk,
+                                     self.window, self.scale, None)
+            ops.talk_mix(spread, self.talk, attn)
+            return
+        plan = ctx.plans.get(PLAN_KEY)
+        if plan is None:                                 # a step put together without asking the parts: plan it now
+            plan = attention_plan(ctx.q_lens, ctx.ctx_lens)
+            plan.arrays = {k: torch.from_numpy(v).to(ctx.device) for k, v in plan.arrays.items()}
+            ctx.plans[PLAN_KEY] = plan
+        tiles64, singles = plan.arrays["tiles64"], plan.arrays["singles"]
+        spread = ctx.empty((T, self.H, self.KV, self.dv))
+        if tiles64.shape[0]:
+            ops.attention_prefill_talk(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles64, spread, self.H, self.chunk,
+                                       self.window, self.scale, None)
+        n = singles.shape[0]
+        if n:
+            longest = plan.host["longest_single"]
+            for bound in (self.chunk, self.window + 64 if self.window > 0 else 0):
+                if bound > 0:
+                    longest = min(longest, bound)
+            groups = self.KV * (-(-(self.H // self.KV) // 16))
+            resident = ops.attention_decode_resident_blocks(self.dk)
+            n_splits = max(1, min(-(-longest // 64), resident // (n * groups), DECODE_MAX_SPLITS))
+            ops.attention_decode_talk(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, spread, self.H,
+                                      self.chunk, self.window, self.scale, None)
+        ops.talk_mix(spread, self.talk, attn)
+
     def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
         T = h.shape[0]
         k_cache, v_cache, table = ctx.kv(cache_layer)
@@ -423,12 +462,9 @@ class ChunkedTalkingAttention(Mixer):
         ops.qk_head_norm_rope_write(proj, self.off_k, self.off_v, self.q_norm, self.k_norm, self.qk_norm_eps, ctx.positions,
                                     ctx.tok_req, table, self.rotary.inv_freq, self.rotary.rot_half, self.rotary.pair_layout, q,
                                     k_cache if write_cache else None, v_cache if write_cache else None, self.H, self.KV,
-                                    self.dk, self.dv)
-        spread = ctx.empty((T, self.H, self.KV, self.dv), torch.float32)
-        ops.attention_talk_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, spread, self.H, self.chunk,
-                                 self.window, self.scale, self.temp)
+                                    self.dk, self.dv, q_head_scale=self.temp)
         attn = ctx.empty((T, self.H * self.dv))
-        ops.talk_mix(spread, self.talk, attn)
+        self.attend(ctx, q, k_cache, v_cache, table, attn)
         linear(ctx, attn, self.wo, out, None, epilogue)
 
     def forward(self, ctx, h, residual, cache_layer, write_cache=True):

@@ -165,7 +165,7 @@ class RoutedExperts(FeedForward):
         """(experts [T, top] int32, weights [T, top] 32-bit) of the rows h."""
         T = h.shape[0]
         z = ctx.empty((T, self.E), torch.float32)
-        ops.gemm_plain(h, self.router, z, None, EPI_NONE)          # 32-bit sums in a fixed order, whatever the step's rows
+        linear(ctx, h, self.router, z, None, EPI_NONE)            # 32-bit sums of exact products (the rows may be bfloat16 roundings)
         ids = torch.empty((T, self.top), dtype=torch.int32, device=ctx.device)
         wts = ctx.empty((T, self.top), torch.float32)
         ops.moe_route(z, self.correction, self.top, self.n_groups, self.keep_groups, ids, wts)
@@ -176,6 +176,17 @@ class RoutedExperts(FeedForward):
     def _run(self, ctx, h, out, add):
         T = h.shape[0]
         ids, wts = self.route(ctx, h)
+        if ctx.fast and ops.grouped_gemm_supported(h, self.w_gate_up) and self.hidden % 8 == 0:
+            # tensor cores: the pairs lie expert by expert in tiles of 128 rows, each tile multiplied by its expert's matrices
+            pos, row_src, tile_expert = ops.moe_plan(ids, self.E)
+            rows = ctx.empty((row_src.numel(), self.dim))
+            ops.gather_rows(h, row_src, self.top, rows)
+            act = ctx.empty((row_src.numel(), self.hidden))
+            ops.gemm_grouped(rows, self.w_gate_up, tile_expert, act, EPI_SWIGLU)
+            y = ctx.empty((row_src.numel(), self.dim), torch.float32)
+            ops.gemm_grouped(act, self.w_down, tile_expert, y, EPI_NONE)
+            ops.moe_combine_rows(y, pos, wts, out, add=add)
+            return
         act = ctx.empty((T * self.top, self.hidden))
         ops.expert_gemm_plain(h, self.top, self.w_gate_up, ids, act, EPI_SWIGLU)
         y = ctx.empty((T * self.top, self.dim), torch.float32)

@@ -213,7 +213,8 @@ class MatrixMemory(_StateMixer):
     S, n and m start at zero. Each head's o is divided by its root mean square, the heads are joined, multiplied by a
     weight per head and channel and by sigmoid(h Wg^T), and projected by Wo. One joined product makes q | k | v | g | i | f;
     a kernel walks the gates (scalars per head) and leaves decays and weighted keys, which the scan of
-    `GatedLinearAttention` consumes. The slot holds S [H, dk, dv], n [H, dk], m [H]."""
+    `GatedLinearAttention` consumes with one more value column, a column of ones: the state's last value column is then the
+    normaliser n and the read-out's last column n . q. The slot holds S | n as [H, dk, dv + 1], and m [H]."""
     RULE = ops.RULE_GLA
 
     def __init__(self, dim: int, n_heads: int, key_dim: int, value_dim: int, gate_cap: float, norm_eps: float, names: Dict[str, str]):
@@ -224,7 +225,7 @@ class MatrixMemory(_StateMixer):
         self.off_k, self.off_v, self.off_g = H * dk, 2 * H * dk, 2 * H * dk + H * dv
         self.off_i = self.off_g + H * dv
         self.off_f = self.off_i + H
-        self.off_n, self.off_m = H * dk * dv, H * dk * dv + H * dk
+        self.off_m = H * dk * (dv + 1)                # the normaliser is the state's last value column
         self.w_in = self.wo = self.norm = self.bias_i = self.bias_f = None
 
     def local_specs(self):
@@ -242,7 +243,14 @@ class MatrixMemory(_StateMixer):
         self.bias_f = to_device_vector(local["bias_f"], dtype, device)
 
     def cache_spec(self):
-        return StateSpec((self.H * self.dk * self.dv + self.H * self.dk + self.H,), "float32")
+        return StateSpec((self.H * self.dk * (self.dv + 1) + self.H,), "float32")
+
+    def _parts(self, q_lens) -> int:
+        n_long = sum(1 for n in q_lens if n >= ops.SCAN_PART_MIN_TOKENS)
+        return ops.recurrent_scan_parts(self.RULE, self.H, self.dk, self.dv + 1, n_long) if n_long else 1
+
+    def _plan_key(self) -> str:
+        return f"recurrence parts {self.RULE} {self.H}x{self.dk}x{self.dv + 1}"
 
     def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
         self._check(write_cache)
@@ -251,16 +259,13 @@ class MatrixMemory(_StateMixer):
         linear(ctx, h, self.w_in, proj, None, EPI_NONE)
         self._joined(proj)
         state = ctx.state(cache_layer)
-        decay = ctx.empty((T, H * dk), torch.float32)
-        keys = ctx.empty((T, H * dk), torch.float32)
-        den = ctx.empty((T, H), torch.float32)
-        ops.memory_gates(proj, 0, self.off_k, self.off_i, self.off_f, self.bias_i, self.bias_f, self.cap, dk ** -0.5, state,
-                         self.off_n, self.off_m, ctx.slots, ctx.cu_q, decay, keys, den, H, dk)
-        o = ctx.empty((T, H * dv), torch.float32)
-        ops.recurrent_scan(ops.RULE_GLA, proj[:, :self.off_k], keys, proj[:, self.off_v:self.off_g], decay, None, dk ** -0.5, state,
-                           ctx.slots, ctx.cu_q, o, H, H, dk, dv, parts=self._step_parts(ctx))
+        decay, keys, values, floor = ops.memory_gates(proj, self.off_k, self.off_v, self.off_i, self.off_f, self.bias_i, self.bias_f,
+                                                      self.cap, state, self.off_m, ctx.slots, ctx.cu_q, H, dk, dv)
+        o = ctx.empty((T, H * (dv + 1)), torch.float32)      # a head's last column: n . q
+        ops.recurrent_scan(ops.RULE_GLA, proj[:, :self.off_k], keys, values, decay, None, dk ** -0.5, state, ctx.slots, ctx.cu_q, o,
+                           H, H, dk, dv + 1, parts=self._step_parts(ctx))
         y = ctx.empty((T, H * dv))
-        ops.head_norm_gate_ext(o, self.norm, proj[:, self.off_g:self.off_i], ops.GATE_SIGMOID, self.eps, y, H, dv, den=den)
+        ops.head_norm_gate_ext(o, self.norm, proj[:, self.off_g:self.off_i], ops.GATE_SIGMOID, self.eps, y, H, dv, floor=floor)
         linear(ctx, y, self.wo, out, None, epilogue)
 
 

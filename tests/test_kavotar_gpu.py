@@ -288,7 +288,7 @@ def test_layer_streams_one_by_one(folders):
     assert len(model.keep_streams) == len(cfg["layers"])
     for i, got in enumerate(model.keep_streams):
         w = want[i].numpy()
-        assert np.abs(got.cpu().numpy() - w).max() <= 2e-5 * np.abs(w).max(), i
+        assert np.abs(got.cpu().numpy() - w).max() <= 1e-4 * np.abs(w).max(), i
 
 
 # ---- mechanisms alone --------------------------------------------------------------------------------------------------
@@ -377,8 +377,8 @@ def test_matrix_memory_kernels_in_portions_with_slots_used_again(H, dk, dv):
         data[rid] = (q, k, v, zi, zf, g)
         o = pk.matrix_memory(q * dk ** -0.5, k, v, pk.soft_cap(zi + bi, cap), pk.log_sigmoid(pk.soft_cap(zf + bf, cap)))
         want[rid] = (pk.rms_unit(o, eps).reshape(T, H * dv) * norm_w * torch.sigmoid(g)).numpy()
-    n_s = H * dk * dv
-    n_state = n_s + H * dk + H
+    n_s = H * dk * (dv + 1)                    # the normaliser is the state's last value column
+    n_state = n_s + H
     state = torch.full((4, n_state + 5), float("nan"), device=DEV)
     slots = {"a": 2, "b": 0}
     for s in slots.values():
@@ -397,12 +397,11 @@ def test_matrix_memory_kernels_in_portions_with_slots_used_again(H, dk, dv):
         T = proj.shape[0]
         cu = i32(np.cumsum([0] + [step[r] for r in rids]))
         sl = i32([slots[r] for r in rids])
-        decay, keys, den = torch.empty(T, H * dk, device=DEV), torch.empty(T, H * dk, device=DEV), torch.empty(T, H, device=DEV)
-        ops.memory_gates(proj, 0, off_k, off_i, off_f, dev(bi), dev(bf), cap, dk ** -0.5, state, n_s, n_s + H * dk, sl, cu, decay, keys, den, H, dk)
-        o = torch.empty(T, H * dv, device=DEV)
-        ops.recurrent_scan(ops.RULE_GLA, proj[:, :off_k], keys, proj[:, off_v:off_g], decay, None, dk ** -0.5, state, sl, cu, o, H, H, dk, dv)
+        decay, keys, values, floor = ops.memory_gates(proj, off_k, off_v, off_i, off_f, dev(bi), dev(bf), cap, state, n_s, sl, cu, H, dk, dv)
+        o = torch.empty(T, H * (dv + 1), device=DEV)
+        ops.recurrent_scan(ops.RULE_GLA, proj[:, :off_k], keys, values, decay, None, dk ** -0.5, state, sl, cu, o, H, H, dk, dv + 1)
         y = torch.empty(T, H * dv, device=DEV)
-        ops.head_norm_gate_ext(o, dev(norm_w), proj[:, off_g:off_i], ops.GATE_SIGMOID, eps, y, H, dv, den=den)
+        ops.head_norm_gate_ext(o, dev(norm_w), proj[:, off_g:off_i], ops.GATE_SIGMOID, eps, y, H, dv, floor=floor)
         y = y.cpu()
         t0 = 0
         for r in rids:
@@ -528,7 +527,7 @@ def test_expert_products_and_their_weighted_sum(dtype):
 
 def test_norm_behind_the_sublayer_pair_mean_cast_and_soft_cap():
     from boring_llm_b200.kernels import ops
-    for rows, d in ((7, 40), (130, 50), (3, 256)):
+    for rows, d in ((7, 40), (130, 50), (3, 256), (5, 4100)):
         x, a, b = rnd(rows, d, seed=1), rnd(rows, d, seed=2, scale=3.0), rnd(rows, d, seed=3, scale=0.1)
         w, wa, wb = rnd(d, seed=4) + 1, rnd(d, seed=5) + 1, rnd(d, seed=6) + 1
         xs = dev(x)
@@ -569,13 +568,64 @@ def test_norm_per_head_rotation_and_cache_write(H, G, dk, dv, rot, layout):
     kc = torch.full((5, G, page, dk), float("nan"), device=DEV)
     vc = torch.full((5, G, page, dv), float("nan"), device=DEV)
     tb = i32([[3, 0, 2, 1]])
+    factor = rnd(H, seed=9)                            # a factor per head on q, of either sign
     ops.qk_head_norm_rope_write(dev(proj), H * dk, (H + G) * dk, dev(qw), dev(kw), eps, positions.to(torch.int32).to(DEV),
                                 torch.zeros(T, dtype=torch.int32, device=DEV), tb, table.inv_freq, table.rot_half, table.pair_layout,
-                                q_out, kc, vc, H, G, dk, dv)
-    np.testing.assert_allclose(q_out.cpu().numpy().reshape(T, H, dk), q.numpy(), atol=3e-5, rtol=1e-4)
+                                q_out, kc, vc, H, G, dk, dv, q_head_scale=dev(factor))
+    np.testing.assert_allclose(q_out.cpu().numpy().reshape(T, H, dk), (q * factor[None, :, None]).numpy(), atol=3e-5, rtol=1e-4)
     pages = [3, 0, 2, 1]
     for t in range(T):
         p = 5 + t
         np.testing.assert_allclose(kc[pages[p // page], :, p % page].cpu().numpy(), k[t].numpy(), atol=3e-5, rtol=1e-4)
         np.testing.assert_allclose(vc[pages[p // page], :, p % page].cpu().numpy(),
                                    proj[t, (H + G) * dk:(H + G) * dk + G * dv].view(G, dv).numpy(), atol=1e-6)
+
+
+@pytest.mark.parametrize("dh,H,G,chunk", [(64, 4, 2, 40), (32, 6, 3, 150), (128, 2, 1, 16), (16, 2, 2, 0), (48, 3, 1, 100)])
+def test_chunk_attention_on_tensor_cores(dh, H, G, chunk):
+    """The two tensor-core shapes (tiles of 64 new tokens; single tokens with their keys cut into slices) against the
+    plain implementation on the same bfloat16 values: planted keys at the chunks' edges, two requests in the batch, one of
+    them decoding, scattered pages with NaN elsewhere."""
+    from boring_llm_b200.kernels import ops
+    from boring_llm_b200.parts.attention import attention_plan
+    T, page = 300, 16
+    bf = lambda t: t.to(torch.bfloat16).double()
+    q, k, v = bf(rnd(T, H, dh, seed=1)), bf(rnd(T, G, dh, seed=2)), bf(rnd(T, G, dh, seed=3))
+    talk = rnd(H, H, seed=4)
+    c = chunk or 1000
+    for qi in (299, 290, 2 * c if 2 * c < T else 150, 2 * c - 1 if 0 < 2 * c - 1 < T else 100, 64, 63):
+        for kj in (qi - qi % c, max(0, qi - qi % c - 1)):
+            k[kj] = bf(k[kj] * 0 + q[qi, 0] / q[qi, 0].norm() * 5.0)
+    want = pk.talking_attention(q, k, v, 0.25, torch.ones(H, dtype=torch.float64), talk, c).numpy()
+    # a second request of 40 tokens that decodes its 41st beside every step of the first
+    q2, k2, v2 = bf(rnd(41, H, dh, seed=5)), bf(rnd(41, G, dh, seed=6)), bf(rnd(41, G, dh, seed=7))
+    want2 = pk.talking_attention(q2, k2, v2, 0.25, torch.ones(H, dtype=torch.float64), talk, c).numpy()[40]
+    order = list(np.random.default_rng(1).permutation(24))
+    kc = torch.full((25, G, page, dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vc = torch.full((25, G, page, dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+    t1, t2 = order[:19], order[19:22]
+    for tab, kk, vv in ((t1, k, v), (t2, k2, v2)):
+        for i in range(kk.shape[0]):
+            kc[tab[i // page], :, i % page] = kk[i].to(torch.bfloat16).to(DEV)
+            vc[tab[i // page], :, i % page] = vv[i].to(torch.bfloat16).to(DEV)
+    tb = i32([t1 + [-1] * 5, t2 + [-1] * 21])
+    got = np.zeros((T, H, dh))
+    at = 0
+    for n, splits in ((200, 1), (90, 1), (1, 1), (1, 3), (1, 2), (1, 1), (1, 4), (1, 1), (1, 1), (1, 2), (1, 1), (1, 1)):
+        q_lens, ctx_lens = [n, 1], [at + n, 41]
+        plan = attention_plan(q_lens, ctx_lens)
+        qq = torch.cat([q[at:at + n].reshape(n, H * dh), q2[40:41].reshape(1, H * dh)]).to(torch.bfloat16).to(DEV).contiguous()
+        spread = torch.full((n + 1, H, G, dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+        cu, ctx = i32([0, n, n + 1]), i32(ctx_lens)
+        tiles, singles = (torch.from_numpy(plan.arrays[a]).to(DEV) for a in ("tiles64", "singles"))
+        if tiles.shape[0]:
+            ops.attention_prefill_talk(qq, kc, vc, cu, ctx, tb, tiles, spread, H, chunk, 0, 0.25, None)
+        ops.attention_decode_talk(qq, kc, vc, cu, ctx, tb, singles, splits, spread, H, chunk, 0, 0.25, None)
+        out = torch.empty(n + 1, H * dh, dtype=torch.bfloat16, device=DEV)
+        ops.talk_mix(spread, dev(talk), out)
+        o = out.float().cpu().numpy().reshape(n + 1, H, dh)
+        assert np.isfinite(o).all()
+        got[at:at + n] = o[:n]
+        np.testing.assert_allclose(o[n], want2, atol=3e-2 * np.abs(want2).max(), rtol=3e-2)
+        at += n
+    np.testing.assert_allclose(got, want, atol=3e-2 * np.abs(want).max(), rtol=3e-2)
