@@ -17,6 +17,10 @@
 // (:3520-3679) and the sharing of key/value reads across a group follows FlashDecodeWarpTail128Kernel
 // (:3793-3925). Scores are scaled after the dot product (src/math.br:319-322); a key j is visible to a query
 // at position p when j <= p and, with a window, j + window > p (:327-328).
+// Options for designs that mix the heads' weights after the softmax (all off for plain attention): every row has a first
+// visible key of its own (a window, a chunk of positions counted from 0, or both), a positive factor per head on the
+// scale, the values are those of a chosen key/value head, and the output is spread over the value heads
+// (bl_attention_prefill_talk, bl_attention_decode_talk: one launch per value head; see attention_talk.cu).
 #include "common.cuh"
 #include "api.h"
 
