@@ -629,3 +629,27 @@ def test_chunk_attention_on_tensor_cores(dh, H, G, chunk):
         np.testing.assert_allclose(o[n], want2, atol=3e-2 * np.abs(want2).max(), rtol=3e-2)
         at += n
     np.testing.assert_allclose(got, want, atol=3e-2 * np.abs(want).max(), rtol=3e-2)
+
+
+def test_the_command_line_and_the_trace_program_on_a_model_folder(folders, tmp_path):
+    """`bin/boring-llm` generates what the plain implementation's arg-max gives, and `bin/trace_run`, started as a user
+    would start it, writes the logits of a mixed trace (float32)."""
+    import os
+    import subprocess
+    import sys
+    folder = folders("A")
+    exe = [sys.executable, os.path.join(helpers.ROOT, "bin", "boring-llm")]
+    prompt = helpers.random_tokens(97, 9, 3)
+    p = subprocess.run(exe + ["--model", folder, "--prompt-tokens", ",".join(map(str, prompt)), "--n-predict", "6", "--dtype", "f32",
+                              "--ctx-size", "64", "--ignore-eos"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr
+    toks = list(prompt)
+    for _ in range(6):
+        toks.append(int(plain_logits(folder, toks)[-1].argmax()))
+    assert p.stdout.strip().splitlines()[-1] == "generated: " + ",".join(map(str, toks[9:]))
+    reqs = {f"t{i}": helpers.random_tokens(97, n, 600 + i) for i, n in enumerate([30, 12, 45])}
+    steps, peak = helpers.mixed_trace(reqs, seed=2, max_live=2)
+    outputs = helpers.run_trace_program(folder, "float32", steps, peak, str(tmp_path / "out"), 97)
+    rows = helpers.collect_rows(steps, outputs)
+    for rid, t in reqs.items():
+        helpers.assert_close(np.stack([rows[(rid, i)] for i in range(len(t))]), plain_logits(folder, t), "float32", rid)
