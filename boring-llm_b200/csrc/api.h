@@ -307,9 +307,9 @@ int bl_memory_gates(const float* proj, int ld, int off_k, int off_v, int off_i, 
                     const void* bias_f, int bf_dtype, float cap, float* state, long long slot_stride, long long off_m,
                     const int* slots, const int* cu_q, int R, int T, float* gates, float* decay, float* k_out, float* v_out,
                     int H, int dk, int dv, void* stream);
-// out[s, t, :] = x[t, :] + (x'[t, :] - x[t, :]) * mu[s, :], s < n_mix, x' the row of the request's token before; for a
+// out[s, t, :] = x[t, :] + (x'[t, :] - x[t, :]) * mu[s, :] (mu 32-bit [n_mix, d]), s < n_mix, x' the row of the request's token before; for a
 // step's first token of a request it is prev + slots[r] * slot_stride [d] (bl_conv_tail_update with two taps keeps it).
-int bl_shift_mix(const float* x, int ld, const void* mu, int mu_dtype, int n_mix, const float* prev, long long slot_stride,
+int bl_shift_mix(const float* x, int ld, const float* mu, int n_mix, const float* prev, long long slot_stride,
                  const int* slots, const int* tok_req, const int* cu_q, void* out, int out_dtype, int T, int d, void* stream);
 // out[t, h] = sum_c u[h, c] * k[t, h, c] * q[t, h, c] (the beta of BL_RULE_BONUS for a bonus per head and key channel).
 int bl_bonus_dot(const float* q, int ldq, const float* k, int ldk, const void* u, int u_dtype, float* out, int T, int H, int dk,

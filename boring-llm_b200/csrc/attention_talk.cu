@@ -104,20 +104,46 @@ attention_talk_plain_kernel(const TT* __restrict__ q, const TT* __restrict__ kc,
     }
 }
 
-// out[t, h, :] = sum_g talk[h, g] * A[t, g, kv(h), :], g ascending; one block per token.
+// out[t, h, :] = sum_g talk[h, g] * A[t, g, kv(h), :], g ascending; one block per token, the mix matrix in shared memory
+// (fetched before the dependent-launch wait: it is a weight), a thread per pair of channels where dv is even.
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+__device__ __forceinline__ void store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+
 template <typename TA, typename TT>
 __global__ void __launch_bounds__(128)
 talk_mix_kernel(const TA* __restrict__ A, const void* __restrict__ talk, int talk_dtype, TT* __restrict__ out, int H, int KV, int dv) {
     bl_pdl_trigger();
+    extern __shared__ float tk[];                      // [H, H]
+    for (int i = threadIdx.x; i < H * H; i += 128) tk[i] = bl_load_any(talk, talk_dtype, i);
     bl_pdl_wait();
+    __syncthreads();
     const int t = blockIdx.x;
     const int rep = H / KV;
+    const size_t g_step = (size_t)KV * dv;             // from head g to head g + 1 in A[t]
+    const TA* At = A + (size_t)t * H * g_step;
+    if ((dv & 1) == 0) {
+        const int half = dv >> 1;
+        for (int e = threadIdx.x; e < H * half; e += 128) {
+            const int h = e / half, d = (e - h * half) * 2;
+            const TA* src = At + (size_t)(h / rep) * dv + d;
+            const float* row = tk + h * H;
+            float a0 = 0.f, a1 = 0.f;
+            for (int g = 0; g < H; ++g) {
+                const float2 v = load2(src + g * g_step);
+                a0 = fmaf(row[g], v.x, a0);
+                a1 = fmaf(row[g], v.y, a1);
+            }
+            store2(out + (size_t)t * H * dv + (size_t)h * dv + d, a0, a1);
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < H * dv; e += 128) {
         const int h = e / dv, d = e % dv;
-        const int c = h / rep;
+        const TA* src = At + (size_t)(h / rep) * dv + d;
         float acc = 0.f;
-        for (int g = 0; g < H; ++g)
-            acc = fmaf(bl_load_any(talk, talk_dtype, (size_t)h * H + g), bl_load(A + (((size_t)t * H + g) * KV + c) * dv + d), acc);
+        for (int g = 0; g < H; ++g) acc = fmaf(tk[h * H + g], bl_load(src + g * g_step), acc);
         bl_store(out + (size_t)t * H * dv + e, acc);
     }
 }
@@ -154,7 +180,9 @@ extern "C" int bl_talk_mix(const void* A, int a_dtype, const void* talk, int tal
     if (T <= 0) return 0;
     if (H <= 0 || KV <= 0 || H % KV != 0 || dv <= 0) BL_FAIL("bl_talk_mix: bad sizes H=%d KV=%d dv=%d", H, KV, dv);
     cudaStream_t s = (cudaStream_t)stream;
-#define BL_GO(TA, TT) BL_CUDA(bl_launch_dependent(talk_mix_kernel<TA, TT>, dim3(T), dim3(128), 0, s, (const TA*)A, talk, talk_dtype, (TT*)out, H, KV, dv))
+    const size_t smem = (size_t)H * H * sizeof(float);
+    if (smem > 48 * 1024) BL_FAIL("bl_talk_mix: %d heads are too many for shared memory", H);
+#define BL_GO(TA, TT) BL_CUDA(bl_launch_dependent(talk_mix_kernel<TA, TT>, dim3(T), dim3(128), smem, s, (const TA*)A, talk, talk_dtype, (TT*)out, H, KV, dv))
     if (a_dtype == BL_F32 && out_dtype == BL_F32) BL_GO(float, float);
     else if (a_dtype == BL_F32 && out_dtype == BL_BF16) BL_GO(float, __nv_bfloat16);
     else if (a_dtype == BL_BF16 && out_dtype == BL_BF16) BL_GO(__nv_bfloat16, __nv_bfloat16);

@@ -539,22 +539,42 @@ memory_expand_kernel(const float* proj, int ld, int off_k, int off_v, const floa
 }
 
 // Token shift: out[s, t, c] = x[t, c] + (x'[t, c] - x[t, c]) * mu[s, c] for s < n_mix, x' the row of the request's token
-// before (from the slot's `prev` [d] for a step's first token: zeros in a fresh slot). One block per token.
+// before (from the slot's `prev` [d] for a step's first token: zeros in a fresh slot). One block per token; four channels
+// a thread (16-byte loads, 8- or 16-byte stores) where the rows allow it.
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const unsigned*>(&lo); pk.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = pk;
+}
+
 template <typename TY>
 __global__ void __launch_bounds__(WARPS * 32)
-shift_mix_kernel(const float* x, int ld, const void* __restrict__ mu, int mu_dtype, int n_mix, const float* prev, size_t slot_stride,
+shift_mix_kernel(const float* x, int ld, const float* __restrict__ mu, int n_mix, const float* prev, size_t slot_stride,
                  const int* __restrict__ slots, const int* __restrict__ tok_req, const int* __restrict__ cu_q, TY* __restrict__ out,
-                 int T, int d) {
+                 int T, int d, int vec) {
     bl_pdl_trigger();
     bl_pdl_wait();
     const int t = blockIdx.x;
     const int r = tok_req[t];
     const float* before = t > cu_q[r] ? x + (size_t)(t - 1) * ld : prev + (size_t)slots[r] * slot_stride;
     const float* cur = x + (size_t)t * ld;
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < d; c += WARPS * 32 * 4) {
+            const float4 xc = *reinterpret_cast<const float4*>(cur + c), xb = *reinterpret_cast<const float4*>(before + c);
+            const float4 dx = make_float4(xb.x - xc.x, xb.y - xc.y, xb.z - xc.z, xb.w - xc.w);
+            for (int s = 0; s < n_mix; ++s) {
+                const float4 m = *reinterpret_cast<const float4*>(mu + (size_t)s * d + c);
+                store4(out + ((size_t)s * T + t) * d + c, fmaf(dx.x, m.x, xc.x), fmaf(dx.y, m.y, xc.y), fmaf(dx.z, m.z, xc.z), fmaf(dx.w, m.w, xc.w));
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < d; c += WARPS * 32) {
         const float xc = cur[c], dx = before[c] - xc;
         for (int s = 0; s < n_mix; ++s)
-            bl_store(out + ((size_t)s * T + t) * d + c, fmaf(dx, bl_load_any(mu, mu_dtype, (size_t)s * d + c), xc));
+            bl_store(out + ((size_t)s * T + t) * d + c, fmaf(dx, mu[(size_t)s * d + c], xc));
     }
 }
 
@@ -783,17 +803,19 @@ extern "C" int bl_memory_gates(const float* proj, int ld, int off_k, int off_v, 
     return 0;
 }
 
-extern "C" int bl_shift_mix(const float* x, int ld, const void* mu, int mu_dtype, int n_mix, const float* prev, long long slot_stride,
+extern "C" int bl_shift_mix(const float* x, int ld, const float* mu, int n_mix, const float* prev, long long slot_stride,
                             const int* slots, const int* tok_req, const int* cu_q, void* out, int out_dtype, int T, int d, void* stream) {
     if (T <= 0) return 0;
     if (d <= 0 || ld < d || n_mix < 1) BL_FAIL("bl_shift_mix: bad sizes d=%d ld=%d mixes=%d", d, ld, n_mix);
     cudaStream_t s = (cudaStream_t)stream;
+    const int vec = d % 4 == 0 && ld % 4 == 0 && slot_stride % 4 == 0 &&
+                    (((uintptr_t)x | (uintptr_t)mu | (uintptr_t)prev | (uintptr_t)out) & 15) == 0;
     if (out_dtype == BL_F32)
-        BL_CUDA(bl_launch_dependent(shift_mix_kernel<float>, dim3(T), dim3(WARPS * 32), 0, s, x, ld, mu, mu_dtype, n_mix, prev,
-                                    (size_t)slot_stride, slots, tok_req, cu_q, (float*)out, T, d));
+        BL_CUDA(bl_launch_dependent(shift_mix_kernel<float>, dim3(T), dim3(WARPS * 32), 0, s, x, ld, mu, n_mix, prev,
+                                    (size_t)slot_stride, slots, tok_req, cu_q, (float*)out, T, d, vec));
     else if (out_dtype == BL_BF16)
-        BL_CUDA(bl_launch_dependent(shift_mix_kernel<__nv_bfloat16>, dim3(T), dim3(WARPS * 32), 0, s, x, ld, mu, mu_dtype, n_mix, prev,
-                                    (size_t)slot_stride, slots, tok_req, cu_q, (__nv_bfloat16*)out, T, d));
+        BL_CUDA(bl_launch_dependent(shift_mix_kernel<__nv_bfloat16>, dim3(T), dim3(WARPS * 32), 0, s, x, ld, mu, n_mix, prev,
+                                    (size_t)slot_stride, slots, tok_req, cu_q, (__nv_bfloat16*)out, T, d, vec));
     else
         BL_FAIL("bl_shift_mix: unknown output dtype %d", out_dtype);
     BL_CHECK_LAUNCH("bl_shift_mix");

@@ -1223,9 +1223,9 @@ def shift_mix(x: torch.Tensor, mu: torch.Tensor, prev: torch.Tensor, slots: torc
     T, d = x.shape
     n_mix = mu.shape[0]
     ld = _rows32(x, "x", T, d)
-    _need(mu, "mu", None, (n_mix, d)); _need(out, "out", None, (n_mix, T, d)); _slot_rows(prev, "prev", d)
+    _need(mu, "mu", torch.float32, (n_mix, d)); _need(out, "out", None, (n_mix, T, d)); _slot_rows(prev, "prev", d)
     _need(slots, "slots", torch.int32); _need(tok_req, "tok_req", torch.int32, (T,)); _need(cu_q, "cu_q", torch.int32)
-    _call(_lib().bl_shift_mix, _p(x), ld, _p(mu), _dt(mu), n_mix, _p(prev), ctypes.c_longlong(prev.stride(0)), _p(slots), _p(tok_req),
+    _call(_lib().bl_shift_mix, _p(x), ld, _p(mu), n_mix, _p(prev), ctypes.c_longlong(prev.stride(0)), _p(slots), _p(tok_req),
           _p(cu_q), _p(out), _dt(out), T, d, _stream())
 
 
