@@ -20,7 +20,7 @@
 // Options for designs that mix the heads' weights after the softmax (all off for plain attention): every row has a first
 // visible key of its own (a window, a chunk of positions counted from 0, or both), a positive factor per head on the
 // scale, the values are those of a chosen key/value head, and the output is spread over the value heads
-// (bl_attention_prefill_talk, bl_attention_decode_talk: one launch per value head; see attention_talk.cu).
+// (bl_attention_prefill_talk, bl_attention_decode_talk: the grid's y counts the value heads; see attention_talk.cu).
 #include "common.cuh"
 #include "api.h"
 
@@ -282,14 +282,19 @@ attention_mma_kernel(const AttnParams p) {
     const int G = p.H / p.KV;
     bl_pdl_trigger();
     int r, kvh, head0, tok0, split = 0;
+    int v_shift = p.v_shift;                                      // spread output: the grid's y also counts the value heads
     if (DECODE) {
         r = p.work[blockIdx.z];
         const int groups16 = (G + 15) / 16;
-        kvh = blockIdx.y / groups16;
-        head0 = kvh * G + (blockIdx.y % groups16) * 16;           // first of up to 16 query heads of this block
+        const int ny = p.KV * groups16;
+        const int by = blockIdx.y % ny;
+        if (p.spread) v_shift = blockIdx.y / ny;
+        kvh = by / groups16;
+        head0 = kvh * G + (by % groups16) * 16;                   // first of up to 16 query heads of this block
         split = blockIdx.x;
         tok0 = 0;
     } else {
+        if (p.spread) v_shift = blockIdx.y;
         // Blocks start in the order of their index: all heads of the last tile, then all heads of the tile before.
         // Late tiles of a request see the most keys: they go first, so that the short ones fill the tail (with the
         // heads outermost, the long tiles of the last heads would start when the SMs are nearly through).
@@ -327,7 +332,7 @@ attention_mma_kernel(const AttnParams p) {
         lo_row[h] = max(lr, 0);
         sc_row[h] = p.head_scale ? p.scale_log2 * p.head_scale[min(head[h], p.H - 1)] : p.scale_log2;
     }
-    const int vh = (kvh + p.v_shift) % p.KV;                      // the key/value head whose VALUES this launch reads
+    const int vh = (kvh + v_shift) % p.KV;                        // the key/value head whose VALUES this block reads
     // the block's range of keys
     const int first_tok = DECODE ? 0 : tok0;
     const int last_tok = DECODE ? 0 : min(q_len, tok0 + KB) - 1;
@@ -795,7 +800,8 @@ extern "C" int bl_attention_decode_tail(const void* q, const void* k_cache, cons
 // The same two shapes for attention whose heads' softmax weights are mixed afterwards (see attention_talk.cu): keys from
 // the query's own chunk of positions (chunk 0: all), a positive factor per head on the scale (head_scale, 32-bit, null:
 // none), and every head's softmax applied to the values of EVERY key/value head: spread [tokens, H, KV, dh] bfloat16.
-// One launch per value head (the scores are worked out again for each; the mix that follows is bl_talk_mix).
+// One launch; the grid's y also counts the value heads (a block works the scores out for its value head again; the mix
+// that follows is bl_talk_mix).
 extern "C" int bl_attention_prefill_talk(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                                          const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
                                          int n_tiles, void* spread, int H, int KV, int dh, int page_size, int chunk, int window,
@@ -811,11 +817,7 @@ extern "C" int bl_attention_prefill_talk(const void* q, const void* k_cache, con
     p.tail = BlAttnTail{nullptr, 0, nullptr, 0};
     p.chunk = chunk; p.head_scale = head_scale; p.spread = 1;
     if ((long long)n_tiles * H > 2147483647LL) BL_FAIL("bl_attention_prefill_talk: %d tiles x %d heads are more blocks than a launch takes", n_tiles, H);
-    for (int v = 0; v < KV; ++v) {
-        p.v_shift = v;
-        if (dispatch<false>(dh, p, dim3(n_tiles * H, 1, 1), (cudaStream_t)stream)) return 1;
-    }
-    return 0;
+    return dispatch<false>(dh, p, dim3(n_tiles * H, KV, 1), (cudaStream_t)stream);      // y: the value head's shift
 }
 
 extern "C" int bl_attention_decode_talk(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
@@ -834,11 +836,8 @@ extern "C" int bl_attention_decode_talk(const void* q, const void* k_cache, cons
     p.tail = BlAttnTail{nullptr, 0, nullptr, 0};
     p.chunk = chunk; p.head_scale = head_scale; p.spread = 1;
     const int G = H / KV;
-    for (int v = 0; v < KV; ++v) {
-        p.v_shift = v;
-        if (dispatch<true>(dh, p, dim3(n_splits, KV * ((G + 15) / 16), n), (cudaStream_t)stream)) return 1;
-    }
-    return 0;
+    if ((long long)KV * KV * ((G + 15) / 16) > 65535) BL_FAIL("bl_attention_decode_talk: %d key/value heads are too many for one launch", KV);
+    return dispatch<true>(dh, p, dim3(n_splits, KV * KV * ((G + 15) / 16), n), (cudaStream_t)stream);   // y: (value head's shift, head group)
 }
 
 // ---------------------------------------------------------------------------------------------------
